@@ -1,0 +1,52 @@
+// Host executor of round tables.
+//
+// Walks a rank's table exactly as the CUDA kernels do (same item order, same
+// flag protocol with epochs, arrival and exit words, bounded waits), but with
+// host threads and std::atomic flags.  It is the CPU oracle for the kernels,
+// lets the flag protocol be exercised under real concurrency on a machine
+// without a GPU, and backs the c10d backend for CPU tensors (ranks in
+// different processes share the flag and data arenas through POSIX shm).
+#pragma once
+#include <atomic>
+#include <cstdint>
+
+#include "plan.h"
+#include "table.h"
+
+namespace sar {
+
+struct HostRankView {           // what one rank can see of every rank
+  int rank = 0, nranks = 0;
+  void* buf[SAR_MAX_RANKS] = {};                       // data buffers (same layout on every rank)
+  std::atomic<uint32_t>* flags[SAR_MAX_RANKS] = {};    // the launch's channel: SAR_FLAG_CAPACITY words each
+  std::atomic<uint32_t>* ctrl[SAR_MAX_RANKS] = {};     // the launch's channel: laid out as SarCtrl
+};
+
+struct HostLaunch {
+  SarGeom geom{};
+  SarDtype dtype = SAR_F32;
+  float scale = 1.0f;
+  uint32_t epoch_base = SAR_VER_STRIDE;   // must grow by SAR_VER_STRIDE per collective
+  double timeout_s = 10.0;
+  double delay_ms = 0.0;                  // sleep before arriving (an injected straggler delay)
+  uint32_t participants = 0;              // ranks that run this collective (exit barrier set)
+};
+
+// Executes block `block` of `nblocks` of this rank's table.  Every block of
+// every rank must be run (concurrently).  Returns a SarStatus.
+uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLaunch& l, int block, int nblocks);
+
+// Convenience: all ranks in this process, `blocks` threads per rank.
+// bufs[r] is rank r's buffer of `count` elements.  delay_ms may be null.
+uint32_t host_execute(const Compiled& c, void* const* bufs, uint64_t count, SarDtype dtype, uint32_t tile_elems,
+                      float scale, int blocks, const double* delay_ms, double timeout_s, int repeats);
+
+// A whole program (one or two phases), every rank's phases in stream order.
+uint32_t host_execute_program(const Program& p, void* const* bufs, uint64_t count, SarDtype dtype, uint32_t tile_elems,
+                              float scale, int blocks, const double* delay_ms, double timeout_s);
+
+uint32_t pick_tile_elems(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t blocks, uint32_t min_bytes,
+                         uint32_t max_bytes);
+SarGeom make_geom(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t tile_elems);
+
+}  // namespace sar

@@ -1,0 +1,142 @@
+// Round table: the device-resident form of a collective schedule.
+//
+// A collective on n ranks over a buffer of `count` elements is a list of ops
+// per rank.  The buffer is cut into `num_chunks` chunks (n-1 for StragglAR,
+// n for ring / halving-doubling); a chunk is cut into tiles of `tile_elems`
+// elements.  Every op works on one chunk (or on one of `parts` equal tile
+// ranges of it) and is executed tile by tile by the rank that owns the table.
+// All data movement is a *pull*: the executing rank loads from peer memory.
+//
+//   SAR_COPY         own[chunk] = peer[chunk]
+//   SAR_REDUCE       own[chunk] = (own[chunk] +) sum over nsrc peers
+//   SAR_REDUCE_PUSH  own[chunk] = peer[chunk] = own[chunk] + peer[chunk]
+//                    (the executing rank also stores the sum into the peer)
+//
+// Synchronisation is one 32-bit flag per (rank, chunk, tile), living in the
+// memory of the rank that owns the slot.  A flag holds `epoch_base + version`,
+// where the version counts how often the slot was rewritten in this
+// collective (0 = the caller's input) and `epoch_base` grows by
+// SAR_VER_STRIDE per collective, so flags never need clearing.  An op names,
+// for every operand, the version it needs; version 0 of a peer slot is covered
+// by that peer's arrival word.  The table is independent of `count`: tile
+// ranges are derived from the chunk geometry at launch.
+//
+// The helpers below are shared by the CUDA kernels and the host executor so
+// that both walk a table in exactly the same order.
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define SAR_HD __host__ __device__ __forceinline__
+#else
+#define SAR_HD inline
+#endif
+
+#define SAR_MAX_RANKS 16
+#define SAR_MAX_CHUNKS 16
+#define SAR_MAX_OPS 256
+#define SAR_VER_STRIDE 32u
+#define SAR_NUM_CHANNELS 4               // independent flag/control sets (0: all ranks, 1: the non-stragglers)
+#define SAR_FLAG_CAPACITY (1u << 18)     // flags per rank and channel
+#define SAR_VEC_BYTES 16
+
+enum SarOpKind : uint8_t { SAR_COPY = 0, SAR_REDUCE = 1, SAR_REDUCE_PUSH = 2 };
+enum SarOpFlag : uint8_t {
+  SAR_F_SCALE = 1,  // multiply the result by the launch's scale (fused AVG / pre-division)
+  SAR_F_LOCAL = 2,  // REDUCE: the own slot is one of the addends
+};
+enum SarDtype : int32_t { SAR_F32 = 0, SAR_BF16 = 1, SAR_F16 = 2 };
+
+// status codes written to the launch's status word (0 = ok)
+enum SarStatus : uint32_t {
+  SAR_OK = 0,
+  SAR_TIMEOUT_ARRIVAL = 1,   // a peer never entered the collective
+  SAR_TIMEOUT_FLAG = 2,      // a tile some op depends on never became ready
+  SAR_TIMEOUT_EXIT = 3,      // a peer never left the collective
+  SAR_TIMEOUT_PIPE = 4,      // an on-chip pipeline barrier never completed
+  SAR_BAD_TABLE = 5,
+  SAR_ABORTED = 6,           // another block of this rank gave up first
+};
+
+struct SarOp {
+  uint8_t kind;        // SarOpKind
+  uint8_t flags;       // SarOpFlag bits
+  uint8_t round;       // schedule round (ops of a rank are sorted by it)
+  uint8_t chunk;
+  uint8_t part;        // this op covers tile range `part` of `parts`
+  uint8_t parts;
+  uint8_t nsrc;        // peers read (1 for COPY / REDUCE_PUSH)
+  uint8_t local_ver;   // version the own slot must have before it is read or overwritten
+  uint8_t post_ver;    // version of the own slot after this op
+  uint8_t push_ver;    // REDUCE_PUSH: version of the peer slot after this op
+  uint8_t pad[2];
+  uint8_t src[SAR_MAX_RANKS];      // peer ranks (physical)
+  uint8_t src_ver[SAR_MAX_RANKS];  // version needed of each peer's slot
+};
+static_assert(sizeof(SarOp) == 12 + 2 * SAR_MAX_RANKS, "SarOp layout");
+
+// Control words of one rank (in its own memory, read by peers).
+struct SarCtrl {
+  uint32_t arrival;    // epoch_base of the newest collective this rank has entered
+  uint32_t exited;     // epoch_base of the newest collective this rank has left
+  uint32_t abort_flag; // set by any block that timed out; makes the others return
+  uint32_t blocks_done;// local counter to find the last block of a launch
+  uint32_t reserved[28];
+};
+
+// Chunk geometry for `count` elements of `esize` bytes in `num_chunks` chunks.
+// Chunks are contiguous, start on 16-byte boundaries and differ by at most one
+// 16-byte vector; the sub-vector tail of the buffer belongs to the last chunk.
+struct SarGeom {
+  uint64_t count;
+  uint32_t esize;
+  uint32_t num_chunks;
+  uint32_t tile_elems;       // multiple of the vector width
+  uint32_t tiles_per_chunk;  // max over chunks (flag stride)
+};
+
+SAR_HD uint64_t sar_chunk_begin(const SarGeom& g, uint32_t c) {
+  const uint64_t vw = SAR_VEC_BYTES / g.esize;
+  const uint64_t nvec = g.count / vw;
+  const uint64_t q = nvec / g.num_chunks, r = nvec % g.num_chunks;
+  if (c >= g.num_chunks) return g.count;
+  return (q * c + (c < r ? c : r)) * vw;
+}
+SAR_HD uint64_t sar_chunk_len(const SarGeom& g, uint32_t c) {
+  return sar_chunk_begin(g, c + 1) - sar_chunk_begin(g, c);
+}
+SAR_HD uint32_t sar_chunk_tiles(const SarGeom& g, uint32_t c) {
+  const uint64_t len = sar_chunk_len(g, c);
+  return (uint32_t)((len + g.tile_elems - 1) / g.tile_elems);
+}
+// tile range [t0, t1) of chunk tiles covered by part `part` of `parts`
+SAR_HD void sar_part_range(uint32_t tiles, uint32_t part, uint32_t parts, uint32_t* t0, uint32_t* t1) {
+  *t0 = (uint32_t)(((uint64_t)tiles * part) / parts);
+  *t1 = (uint32_t)(((uint64_t)tiles * (part + 1)) / parts);
+}
+SAR_HD uint32_t sar_op_tiles(const SarGeom& g, const SarOp& op) {
+  uint32_t t0, t1;
+  sar_part_range(sar_chunk_tiles(g, op.chunk), op.part, op.parts, &t0, &t1);
+  return t1 - t0;
+}
+SAR_HD uint32_t sar_flag_index(const SarGeom& g, uint32_t chunk, uint32_t tile) {
+  return chunk * g.tiles_per_chunk + tile;
+}
+// wrap-safe "flag has reached target"
+SAR_HD bool sar_reached(uint32_t flag, uint32_t target) { return (int32_t)(flag - target) >= 0; }
+
+// Work items of one rank.  The ops of one round are interleaved tile by tile
+// (item k of a round with m ops is tile k/m of op k%m, skipping ops that have
+// run out of tiles), and rounds follow one another.  Block b of G executes the
+// items b, b+G, b+2G, ... in this order, which keeps a rank's blocks on the
+// same round and lets every op of a round progress at the same rate.
+struct SarRoundSpan {
+  uint16_t op_begin, op_end;  // ops [op_begin, op_end) belong to this round
+  uint32_t max_tiles;         // max tiles over these ops
+  uint64_t item_begin;        // first item index of the round (dense numbering below)
+};
+// Items are numbered densely per round as k = tile * m + j (j = op within the
+// round); an item whose op has fewer tiles than `tile` is void and skipped.
+SAR_HD uint64_t sar_round_items(const SarRoundSpan& r) {
+  return (uint64_t)r.max_tiles * (uint32_t)(r.op_end - r.op_begin);
+}

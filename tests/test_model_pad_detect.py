@@ -1,0 +1,96 @@
+"""Analytical model, padding helper and straggler detection."""
+import io
+import math
+from contextlib import redirect_stdout
+
+import pytest
+
+from stragglar_b200 import detect, pad, simulate
+
+
+def test_reference_speedups():
+    sp, rhd, direct, ring = simulate.compute_speedups(simulate.POWERS_OF_TWO)
+    assert [round(float(x), 3) for x in sp] == [1.127, 1.363, 1.565, 1.718, 1.826, 1.897, 1.941]
+    assert [round(float(x), 3) for x in rhd] == [1.002, 1.006, 1.016, 1.036, 1.078, 1.162, 1.331]
+    assert [round(float(x), 3) for x in direct] == [0.753, 0.589, 0.478, 0.404, 0.356, 0.332, 0.335]
+    sp, rhd, direct, ring = simulate.compute_speedups(simulate.IN_BETWEEN)
+    assert [round(float(x), 3) for x in sp] == [1.192, 1.346, 1.635, 1.617, 1.743, 1.829]
+    assert [round(float(x), 3) for x in rhd] == [0.670, 0.675, 0.685, 0.706, 0.748, 0.833]
+
+
+def test_absolute_times_n8():
+    s, rhd, ring, direct = simulate.compute_costs([8])
+    assert round(float(s[0]), 3) == 2.884 and round(float(ring[0]), 3) == 3.931
+    assert round(float(rhd[0]), 3) == 3.907 and round(float(direct[0]), 3) == 6.676
+
+
+def test_model_rounds_match_synthesizer():
+    from stragglar_b200.synth import synthesize
+    for n in (4, 8, 16):
+        assert len(synthesize(n)) == simulate.stragglar_rounds(n)
+    assert len(synthesize(6)) == simulate.NONPOW2_ROUNDS[6]
+
+
+def test_printed_lines():
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        simulate.main([])
+    lines = buf.getvalue().splitlines()
+    assert lines[0].startswith("Speedups for powers of two: [") and lines[1].startswith(
+        "Speedups for non-power-of-two values: [")
+    assert len(lines) == 2
+
+
+def test_b200_model_is_faster_link():
+    a = simulate.compute_costs([8], simulate.LinkModel.b200())[0][0]
+    b = simulate.compute_costs([8])[0][0]
+    assert a < b
+
+
+def test_padding_values():
+    assert pad.padded_sizes(8)[-1] == 1073744896 and pad.padded_sizes(4)[-1] == 1073743872
+    assert pad.padded_sizes(8)[0] == 265216
+    for n in (2, 4, 6, 8):
+        for raw, p in zip(pad.BUFFER_SIZES, pad.padded_sizes(n)):
+            assert p >= raw and p % ((n - 1) * 1024) == 0 and p // (n - 1) > raw // (n - 1)
+
+
+def test_pad_cli():
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        assert pad.main(["pad", "8"]) == 0
+    assert buf.getvalue().splitlines()[1].startswith("Padded buffer sizes:  265216 1053696")
+    assert pad.main(["pad"]) == 1
+
+
+LOG = """noise
+\x1b[92mRank 1 | Step 0 | Forward Time: 1.0 ms | Backward Time: 2.0 ms  | Loss: 5.5 | Iteration Time: 6.0 ms | AR Time: 900.00 ms | AR Buffer Size: 1.00 KB\x1b[0m
+Rank 0 | Step 0 | Forward Time: 1.0 ms | AR Time: 1000.00 ms | x Rank 2 | Step 0 | Forward Time: 1.0 ms | AR Time: 800.00 ms | y
+Rank 0 | Step 1 | Forward Time: 1.0 ms | AR Time: 141.00 ms | x
+Rank 1 | Step 1 | Forward Time: 1.0 ms | AR Time: 146.00 ms | x
+Rank 2 | Step 1 | Forward Time: 1.0 ms | AR Time: 118.00 ms | x
+Rank 0 | Step 2 | Forward Time: 1.0 ms | AR Time: 145.00 ms | x
+Rank 1 | Step 2 | Forward Time: 1.0 ms | AR Time: 139.00 ms | x
+Rank 2 | Step 2 | Forward Time: 1.0 ms | AR Time: 118.50 ms | x
+"""
+
+
+def test_detect_from_log():
+    table = detect.parse_ar_times(LOG.splitlines(True))
+    assert table[0] == {1: 900.0, 0: 1000.0, 2: 800.0}
+    rep = detect.analyse(table)
+    assert rep.straggler == 2 and rep.share[2] == 100.0
+    assert rep.delays_ms == [pytest.approx(23.0), pytest.approx(20.5)]
+    assert rep.median_delay_ms == pytest.approx(21.75)
+
+
+def test_online_detector():
+    d = detect.OnlineDetector(4, window=5, threshold=0.8)
+    for _ in range(4):
+        d.update([140, 139, 118, 130])
+    assert d.recommendation() is None
+    d.update([140, 100, 118, 130])
+    assert d.recommendation() == 2
+    a = detect.OnlineDetector(3, window=2, arrival=True)
+    a.update([0.1, 0.2, 5.0]); a.update([0.1, 0.3, 7.0])
+    assert a.recommendation() == 2
