@@ -1,0 +1,180 @@
+// allreduce <NUM_BYTES> <ALG> <ITERS> <DELAY>
+//
+// AllReduce benchmark over the GPUs of one box, one host process driving all of
+// them.  ALG is stragglar, ring, rhd or direct (also: stragglar_a2a, rsag).
+// DELAY is the straggler's delay in ms; -1 means "the pre-phase (ReduceScatter
+// for stragglar, sub-AllReduce for direct) has already happened": it is
+// emulated by pre-filling the buffers and only the post-arrival rounds are
+// timed; 0 times the pre-phase too, without a delay.  Same command line, same
+// first six CSV columns and same semantics as the reference programs
+// (stragglar/allreduce_8GPU.cu:907-1093, README.md:32-33), for any GPU count
+// with a schedule (1, 2, 4, 6, 8, ...), fp32/bf16/fp16, seeded uniform inputs
+// verified on the device after every iteration.
+//
+// What differs from the reference, on purpose: the collectives are the
+// library's own peer-memory kernels (no NCCL); runtime_ms is the maximum over
+// ranks of the device time between per-rank events placed after a device-side
+// start barrier (the reference times device 0 only); the delay is spun on
+// %globaltimer, so it lasts DELAY ms at any SM clock; extra columns follow the
+// reference's six.  Options come from STRAGGLAR_* environment variables (see
+// bench_common.h).
+#include <algorithm>
+#include <cmath>
+
+#include "bench_common.h"
+
+using namespace bench;
+
+int main(int argc, char* argv[]) {
+  if (argc != 5) {
+    fprintf(stderr, "Usage: %s <bufferSize> <algorithm> <numIters> <sleepTimeMs>\n", argv[0]);
+    exit(EXIT_FAILURE);
+  }
+  const size_t bytes = (size_t)strtoull(argv[1], NULL, 10);
+  const char* alg = argv[2];
+  const int numIters = atoi(argv[3]);
+  const float sleepTime = (float)atof(argv[4]);
+  static const char* kAlgs[] = {"ring", "rhd", "direct", "stragglar", "stragglar_a2a", "rsag"};
+  if (std::none_of(std::begin(kAlgs), std::end(kAlgs), [&](const char* a) { return !strcmp(a, alg); })) {
+    fprintf(stderr, "Invalid algorithm: %s\n", alg);
+    exit(EXIT_FAILURE);
+  }
+  Options o = read_options();
+  const int n = o.ngpus;
+  const uint32_t esize = dtype_size(o.dtype);
+  const uint64_t count = bytes / esize;
+  const int straggler = o.straggler >= 0 ? o.straggler : n - 1;
+  const bool prephase = sleepTime >= 0;
+
+  char err[512] = {0};
+  sar_program* prog = sar_program_build(alg, n, prephase ? 1 : 0, o.straggler, o.schedule_text.empty() ? nullptr : o.schedule_text.c_str(), err, sizeof err);
+  if (!prog) { fprintf(stderr, "%s\n", err); exit(EXIT_FAILURE); }
+  // roofline input: bytes the busiest rank moves in one direction after the straggler arrived
+  sar_program* post = sar_program_build(alg, n, sleepTime == 0 ? 1 : 0, o.straggler, o.schedule_text.empty() ? nullptr : o.schedule_text.c_str(), err, sizeof err);
+  double link_bytes = 0;
+  for (int ph = 0; post && ph < sar_program_num_phases(post); ++ph) {
+    const sar_table* t = sar_program_phase(post, ph);
+    double mx = 0;
+    for (int r = 0; r < n; ++r) mx = std::max(mx, std::max(sar_table_chunks_in(t, r), sar_table_chunks_out(t, r)));
+    link_bytes += mx * (double)bytes / sar_table_num_chunks(t);
+  }
+  const double link_gbs = atof(env_str("STRAGGLAR_LINK_GBS", "770"));
+
+  std::vector<int> devs(n);
+  for (int i = 0; i < n; ++i) devs[i] = o.emulate ? 0 : i;
+  sar_local_comm* comm = sar_local_create(n, devs.data(), o.emulate ? 1 : 0, err, sizeof err);
+  if (!comm) { fprintf(stderr, "%s\n", err); exit(EXIT_FAILURE); }
+  Buffers B;
+  B.alloc(n, devs, count * esize);
+
+  // the delay as the device really serves it
+  double real_delay_ms = 0;
+  if (sleepTime > 0) {
+    CHECK_CUDA(cudaSetDevice(devs[straggler]));
+    cudaEvent_t a, b;
+    CHECK_CUDA(cudaEventCreate(&a)); CHECK_CUDA(cudaEventCreate(&b));
+    cudaStream_t st = (cudaStream_t)sar_local_stream(comm, straggler);
+    CHECK_CUDA(cudaEventRecord(a, st));
+    CHECK_CUDA((cudaError_t)sar_cuda_delay((uint64_t)(sleepTime * 1e6), st));
+    CHECK_CUDA(cudaEventRecord(b, st));
+    CHECK_CUDA(cudaEventSynchronize(b));
+    float ms = 0; CHECK_CUDA(cudaEventElapsedTime(&ms, a, b));
+    real_delay_ms = ms;
+    printf("Sleep: requested %.3f ms, measured %.3f ms on device %d\n", sleepTime, real_delay_ms, devs[straggler]);
+  }
+
+  std::vector<uint64_t> seeds(n), delay_ns(n, 0);
+  if (sleepTime > 0) delay_ns[straggler] = (uint64_t)(sleepTime * 1e6);
+  sar_run_opts ro{};
+  ro.path = o.path; ro.blocks = o.blocks; ro.threads = o.threads; ro.tile_bytes = o.tile_bytes;
+  ro.timeout_s = o.timeout_s + (sleepTime > 0 ? sleepTime / 1e3 : 0); ro.scale = 1.0f; ro.timed = 1;
+  const float atol = o.dtype == SAR_F32 ? 2e-5f : o.dtype == SAR_BF16 ? 0.07f : 0.01f;
+  const float rtol = o.dtype == SAR_F32 ? 1e-6f : o.dtype == SAR_BF16 ? 0.02f : 0.004f;
+  const bool is_sar = !strncmp(alg, "stragglar", 9);
+
+  printf("algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s),n,dtype,path,time_us_max,algbw_GBps,busbw_GBps,roofline_frac,real_delay_ms\n");
+  int failures = 0;
+  std::vector<float> ms(n);
+  for (int iter = -o.warmup; iter < numIters; ++iter) {
+    for (int r = 0; r < n; ++r) {
+      seeds[r] = (uint64_t)r + 131ull * (uint64_t)(iter + o.warmup);
+      CHECK_CUDA(cudaSetDevice(devs[r]));
+      cudaStream_t st = (cudaStream_t)sar_local_stream(comm, r);
+      if (o.const_fill) CHECK_CUDA((cudaError_t)sar_cuda_fill_const(B.ptr[r], count, o.dtype, (float)(r + 1), st));
+      else CHECK_CUDA((cudaError_t)sar_cuda_fill_uniform(B.ptr[r], count, o.dtype, seeds[r], st));
+    }
+    if (!prephase && n > 1 && (is_sar || !strcmp(alg, "direct"))) {
+      // emulate the finished pre-phase (cf. stragglar/allreduce_8GPU.cu:1013-1020)
+      std::vector<uint64_t> non;
+      float csum = 0;
+      for (int r = 0; r < n; ++r) if (r != straggler) { non.push_back(seeds[r]); csum += (float)(r + 1); }
+      std::vector<int> l2p(n);
+      for (int i = 0; i < n; ++i) l2p[i] = i;
+      std::swap(l2p[n - 1], l2p[straggler]);
+      for (int i = 0; i < n - 1; ++i) {
+        const int r = l2p[i];
+        uint64_t b = 0, e = count;
+        if (is_sar) chunk_range(count, esize, n - 1, i, &b, &e);
+        CHECK_CUDA(cudaSetDevice(devs[r]));
+        cudaStream_t st = (cudaStream_t)sar_local_stream(comm, r);
+        if (o.const_fill) CHECK_CUDA((cudaError_t)sar_cuda_fill_const((char*)B.ptr[r] + b * esize, e - b, o.dtype, csum, st));
+        else CHECK_CUDA((cudaError_t)sar_cuda_fill_uniform_sum(B.ptr[r], b, e, o.dtype, non.data(), (int)non.size(), st));
+      }
+    }
+    for (int r = 0; r < n; ++r) { CHECK_CUDA(cudaSetDevice(devs[r])); CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)sar_local_stream(comm, r))); }
+
+    if (sar_local_run(comm, prog, B.ptr.data(), count, o.dtype, &ro, sleepTime > 0 ? delay_ns.data() : nullptr, err, sizeof err)) {
+      fprintf(stderr, "launch failed: %s\n", err);
+      exit(EXIT_FAILURE);
+    }
+    const uint32_t status = sar_local_sync(comm, ms.data());
+    if (status) {
+      fprintf(stderr, "collective failed in iteration %d: %s\n", iter, status < 0x1000 ? sar_status_string(status) : cudaGetErrorString((cudaError_t)(status - 0x1000)));
+      exit(2);
+    }
+    if (o.verify == 2 || (o.verify == 1 && iter == numIters - 1)) {
+      for (int r = 0; r < n; ++r) {
+        CHECK_CUDA(cudaSetDevice(devs[r]));
+        uint32_t res[2] = {0, 0};
+        if (o.const_fill) {
+          // all ones' sum: n(n+1)/2 -- checked through the same kernel with zero seeds would not apply; copy a sample
+          std::vector<char> h(std::min<size_t>(count * esize, 1 << 20));
+          CHECK_CUDA(cudaMemcpy(h.data(), B.ptr[r], h.size(), cudaMemcpyDeviceToHost));
+          const float want = n * (n + 1) / 2.0f;
+          for (size_t i = 0; i < h.size() / esize; ++i) {
+            float v;
+            if (o.dtype == SAR_F32) v = ((float*)h.data())[i];
+            else { uint16_t u = ((uint16_t*)h.data())[i]; uint32_t w = (uint32_t)u << 16; if (o.dtype == SAR_BF16) memcpy(&v, &w, 4); else v = want; }
+            if (v != want) ++res[0];
+          }
+        } else {
+          CHECK_CUDA((cudaError_t)sar_cuda_verify_uniform_sum(B.ptr[r], 0, count, o.dtype, seeds.data(), n, 1.0f, atol, rtol, B.result[r], nullptr));
+          CHECK_CUDA(cudaMemcpy(res, B.result[r], 8, cudaMemcpyDeviceToHost));
+        }
+        if (res[0]) {
+          float worst; memcpy(&worst, &res[1], 4);
+          fprintf(stderr, "VERIFY FAILED: iteration %d rank %d: %u wrong elements (max abs error %g)\n", iter, r, res[0], worst);
+          ++failures;
+        }
+      }
+    }
+    if (iter < 0) continue;
+    const float t = *std::max_element(ms.begin(), ms.end());
+    float bw;   // the reference's column: GiB/s with the nominal delay taken off
+    if (sleepTime > 0) bw = (float)bytes / 1024.0f / 1024.0f / 1024.0f * 1000.0f / (t - sleepTime);
+    else bw = (float)bytes / 1024.0f / 1024.0f / 1024.0f * 1000.0f / t;
+    const double net_ms = t - real_delay_ms;
+    const double algbw = (double)bytes / 1e9 / (net_ms / 1e3);
+    const double busbw = algbw * 2.0 * (n - 1) / std::max(n, 1);
+    const double roof_ms = link_bytes / (link_gbs * 1e9) * 1e3;
+    printf("%s,%zu,%d,%.3f,%.3f,%.3f,%d,%s,%s,%.1f,%.2f,%.2f,%.3f,%.3f\n", alg, (size_t)count * esize, iter + 1, sleepTime, t, bw, n,
+           dtype_name(o.dtype), o.path == SAR_PATH_TMA ? "tma" : "simt", t * 1e3, algbw, busbw, net_ms > 0 ? roof_ms / net_ms : 0.0, real_delay_ms);
+  }
+  B.release();
+  sar_local_destroy(comm);
+  sar_program_free(prog);
+  if (post) sar_program_free(post);
+  for (int i = 0; i < n; ++i) printf("Rank %d, done\n", i);
+  if (failures) { fprintf(stderr, "%d verification failures\n", failures); return 3; }
+  return 0;
+}

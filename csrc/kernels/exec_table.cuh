@@ -1,0 +1,726 @@
+// Persistent table-executing collective kernel for sm_100a.
+//
+// One launch per rank and collective: G resident thread blocks walk the rank's
+// op table (csrc/core/table.h) and move data with loads from and stores to
+// peer memory over NVLink / NVSwitch.  There is no NCCL call and no host round
+// trip between rounds: per-tile flags in the slot owner's memory order the
+// rounds, so a tile is forwarded as soon as it is final and the rounds of the
+// schedule pipeline into one another.  The reduction is fused into the
+// transfer: a reduce op loads the peers' tiles and the own tile, adds in fp32
+// and stores the rounded sum once (and, for a straggler matching, also into
+// the peer).  Replaces the ncclSend/ncclRecv + reduce_add sequence of the
+// reference (stragglar/allreduce_8GPU.cu:29-34,555-874).
+//
+// Two data paths execute the same table:
+//   * simt: every thread moves 16-byte vectors with ld.relaxed.sys / st;
+//   * tma:  a producer thread streams tiles from peer memory into a shared
+//           memory ring with bulk async copies (cp.async.bulk + mbarrier
+//           complete_tx), consumer warps add in place, and bulk stores write
+//           the result to local and peer memory.  Few threads keep hundreds of
+//           KB in flight per block.
+//
+// Every wait (peer arrival, tile flag, pipeline barrier, exit) is bounded by a
+// %globaltimer deadline.  On expiry the block records a SarStatus, raises the
+// rank's abort word so that its other blocks stop too, waits for its own bulk
+// copies in flight and returns; nothing traps and nothing spins forever.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../core/table.h"
+#include "sar_params.h"
+
+namespace sar_dev {
+
+// ------------------------------------------------------------------ primitives
+__device__ __forceinline__ uint64_t globaltimer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// 16-byte load that is coherent at system scope (never served from a stale L1 line)
+__device__ __forceinline__ uint4 ld_vec_sys(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_vec(void* p, uint4 v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// ----------------------------------------------------------- element handling
+template <typename T> struct Vec;  // 16 bytes of T <-> floats
+template <> struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ static void unpack(uint4 v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+  }
+  __device__ static uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+  __device__ static float load1(const void* p) { return __uint_as_float(ld_relaxed_sys((const uint32_t*)p)); }
+  __device__ static void store1(void* p, float v) { *(volatile float*)p = v; }
+};
+template <> struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void unpack(uint4 v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+  __device__ static uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ static float load1(const void* p) {
+    unsigned short h;
+    asm volatile("ld.relaxed.sys.global.u16 %0, [%1];" : "=h"(h) : "l"(p) : "memory");
+    return __uint_as_float((uint32_t)h << 16);
+  }
+  __device__ static void store1(void* p, float v) {
+    __nv_bfloat16 h = __float2bfloat16_rn(v);
+    *(volatile unsigned short*)p = *reinterpret_cast<unsigned short*>(&h);
+  }
+};
+template <> struct Vec<__half> {
+  static constexpr int N = 8;
+  __device__ static void unpack(uint4 v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ static uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ static float load1(const void* p) {
+    unsigned short h;
+    asm volatile("ld.relaxed.sys.global.u16 %0, [%1];" : "=h"(h) : "l"(p) : "memory");
+    return __half2float(*reinterpret_cast<__half*>(&h));
+  }
+  __device__ static void store1(void* p, float v) {
+    __half h = __float2half_rn(v);
+    *(volatile unsigned short*)p = *reinterpret_cast<unsigned short*>(&h);
+  }
+};
+
+// --------------------------------------------------------------- bounded waits
+struct WaitCtx {
+  uint64_t deadline;        // %globaltimer value after which waits give up
+  uint32_t* abort_flag;     // this rank's abort word (local memory)
+  uint32_t* status;
+};
+__device__ __forceinline__ void record_failure(const WaitCtx& w, uint32_t code) {
+  if (w.status) atomicCAS(w.status, 0u, code);
+  atomicExch(w.abort_flag, 1u);
+  __threadfence_system();
+}
+// Spin until *p reaches target; false on abort or deadline (failure recorded).
+__device__ __noinline__ bool wait_word(const uint32_t* p, uint32_t target, const WaitCtx& w, uint32_t fail_code) {
+  if (sar_reached(ld_acquire_sys(p), target)) return true;
+  uint32_t ns = 20;
+  for (uint64_t it = 0;; ++it) {
+    if (sar_reached(ld_acquire_sys(p), target)) return true;
+    if ((it & 15) == 15) {
+      if (*(volatile uint32_t*)w.abort_flag) return false;
+      if (globaltimer() > w.deadline) { record_failure(w, fail_code); return false; }
+    }
+    __nanosleep(ns);
+    if (ns < 400) ns += ns >> 1;
+  }
+}
+
+// An item of the rank's work list, resolved against the geometry.
+struct Item {
+  const SarOp* op;
+  uint32_t tile;        // tile index within the chunk
+  uint32_t fidx;        // flag index
+  uint64_t elem0;       // first element
+  uint32_t nelem;       // elements in the tile
+};
+
+// Iterates the items of block `block` of `nblocks` in table order.
+struct ItemWalker {
+  const SarLaunchParams* P;
+  uint32_t block, nblocks;
+  uint32_t ri;            // current round index
+  uint32_t ob, m, max_tiles;
+  uint64_t items, k, item_base;
+  __device__ void init(const SarLaunchParams* p, uint32_t b, uint32_t nb) {
+    P = p; block = b; nblocks = nb; ri = 0; item_base = 0;
+    load_round();
+  }
+  __device__ void load_round() {
+    while (ri < P->num_rounds) {
+      ob = P->round_begin[ri];
+      const uint32_t oe = P->round_begin[ri + 1];
+      m = oe - ob;
+      max_tiles = 0;
+      for (uint32_t o = ob; o < oe; ++o) {
+        const uint32_t t = sar_op_tiles(P->geom, P->ops[o]);
+        max_tiles = t > max_tiles ? t : max_tiles;
+      }
+      items = (uint64_t)max_tiles * m;
+      k = ((uint64_t)block + nblocks - (item_base % nblocks)) % nblocks;
+      if (k < items) return;
+      item_base += items;
+      ++ri;
+    }
+  }
+  // false when the table is exhausted
+  __device__ bool next(Item* it) {
+    while (ri < P->num_rounds) {
+      while (k < items) {
+        const SarOp* op = P->ops + ob + (uint32_t)(k % m);
+        const uint32_t lt = (uint32_t)(k / m);
+        k += nblocks;
+        uint32_t t0, t1;
+        sar_part_range(sar_chunk_tiles(P->geom, op->chunk), op->part, op->parts, &t0, &t1);
+        if (lt >= t1 - t0) continue;
+        const uint32_t tile = t0 + lt;
+        const uint64_t cb = sar_chunk_begin(P->geom, op->chunk), cl = sar_chunk_len(P->geom, op->chunk);
+        const uint64_t e0 = cb + (uint64_t)tile * P->geom.tile_elems;
+        uint64_t e1 = e0 + P->geom.tile_elems;
+        if (e1 > cb + cl) e1 = cb + cl;
+        it->op = op; it->tile = tile; it->fidx = sar_flag_index(P->geom, op->chunk, tile);
+        it->elem0 = e0; it->nelem = (uint32_t)(e1 - e0);
+        return true;
+      }
+      item_base += items;
+      ++ri;
+      load_round();
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ bool op_reads_local(const SarOp* op) {
+  return op->kind == SAR_REDUCE_PUSH || (op->kind == SAR_REDUCE && (op->flags & SAR_F_LOCAL));
+}
+
+// Waits (one thread) until every operand of the item is ready.
+__device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const WaitCtx& w, uint32_t* arrived_mask) {
+  const SarOp* op = it.op;
+  for (int q = 0; q < op->nsrc; ++q) {
+    const int src = op->src[q];
+    if (!(*arrived_mask >> src & 1)) {
+      if (!wait_word(&P.comm.ctrl[src]->arrival, P.epoch_base, w, SAR_TIMEOUT_ARRIVAL)) return false;
+      *arrived_mask |= 1u << src;
+    }
+    if (op->src_ver[q] && !wait_word(P.comm.flags[src] + it.fidx, P.epoch_base + op->src_ver[q], w, SAR_TIMEOUT_FLAG))
+      return false;
+  }
+  if (op->local_ver && !wait_word(P.comm.flags[P.rank] + it.fidx, P.epoch_base + op->local_ver, w, SAR_TIMEOUT_FLAG))
+    return false;
+  return true;
+}
+
+__device__ __forceinline__ void publish_item(const SarLaunchParams& P, const SarOp* op, uint32_t fidx) {
+  st_release_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
+  if (op->kind == SAR_REDUCE_PUSH) st_release_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
+}
+
+// Sub-vector tail (fewer than 16 bytes) of a tile, element by element.
+template <typename T>
+__device__ void scalar_elems(const SarLaunchParams& P, const SarOp* op, uint64_t e0, uint32_t n) {
+  char* own = (char*)P.comm.buf[P.rank];
+  const bool local = op_reads_local(op);
+  const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
+  for (uint32_t i = 0; i < n; ++i) {
+    const uint64_t off = (e0 + i) * sizeof(T);
+    float acc;
+    if (op->kind == SAR_COPY) acc = Vec<T>::load1((char*)P.comm.buf[op->src[0]] + off);
+    else {
+      acc = local ? Vec<T>::load1(own + off) : 0.0f;
+      for (int q = 0; q < op->nsrc; ++q) acc += Vec<T>::load1((char*)P.comm.buf[op->src[q]] + off);
+      acc *= scale;
+    }
+    Vec<T>::store1(own + off, acc);
+    if (op->kind == SAR_REDUCE_PUSH) Vec<T>::store1((char*)P.comm.buf[op->src[0]] + off, acc);
+  }
+}
+
+// ------------------------------------------------------------------- simt path
+template <typename T, int UNROLL>
+__device__ void simt_tile(const SarLaunchParams& P, const Item& it) {
+  constexpr int N = Vec<T>::N;
+  const SarOp* op = it.op;
+  const uint32_t nvec = it.nelem / N;
+  const uint64_t byte0 = it.elem0 * sizeof(T);
+  char* own = (char*)P.comm.buf[P.rank] + byte0;
+  const uint32_t tid = threadIdx.x, nth = blockDim.x;
+  if (op->kind == SAR_COPY) {
+    const char* src = (const char*)P.comm.buf[op->src[0]] + byte0;
+    uint32_t v = tid;
+    for (; v + (UNROLL - 1) * nth < nvec; v += UNROLL * nth) {
+      uint4 r[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) r[u] = ld_vec_sys(src + (size_t)(v + u * nth) * 16);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) st_vec(own + (size_t)(v + u * nth) * 16, r[u]);
+    }
+    for (; v < nvec; v += nth) st_vec(own + (size_t)v * 16, ld_vec_sys(src + (size_t)v * 16));
+  } else {
+    const bool local = op_reads_local(op);
+    const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
+    const int nsrc = op->nsrc;
+    char* push = op->kind == SAR_REDUCE_PUSH ? (char*)P.comm.buf[op->src[0]] + byte0 : nullptr;
+    if (nsrc == 1) {
+      // pairwise: own (+) one peer, unrolled over vectors
+      const char* src = (const char*)P.comm.buf[op->src[0]] + byte0;
+      uint32_t v = tid;
+      for (; v + (UNROLL - 1) * nth < nvec; v += UNROLL * nth) {
+        uint4 a[UNROLL], b[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) a[u] = ld_vec_sys(src + (size_t)(v + u * nth) * 16);
+        if (local) {
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) b[u] = ld_vec_sys(own + (size_t)(v + u * nth) * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          float fa[N], fb[N];
+          Vec<T>::unpack(a[u], fa);
+          if (local) {
+            Vec<T>::unpack(b[u], fb);
+#pragma unroll
+            for (int i = 0; i < N; ++i) fa[i] += fb[i];
+          }
+#pragma unroll
+          for (int i = 0; i < N; ++i) fa[i] *= scale;
+          const uint4 o = Vec<T>::pack(fa);
+          st_vec(own + (size_t)(v + u * nth) * 16, o);
+          if (push) st_vec(push + (size_t)(v + u * nth) * 16, o);
+        }
+      }
+      for (; v < nvec; v += nth) {
+        float fa[N], fb[N];
+        Vec<T>::unpack(ld_vec_sys(src + (size_t)v * 16), fa);
+        if (local) {
+          Vec<T>::unpack(ld_vec_sys(own + (size_t)v * 16), fb);
+#pragma unroll
+          for (int i = 0; i < N; ++i) fa[i] += fb[i];
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) fa[i] *= scale;
+        const uint4 o = Vec<T>::pack(fa);
+        st_vec(own + (size_t)v * 16, o);
+        if (push) st_vec(push + (size_t)v * 16, o);
+      }
+    } else {
+      // several peers (reduce-scatter stage): all sources of a vector in flight at once
+      for (uint32_t v = tid; v < nvec; v += nth) {
+        float acc[N];
+        if (local) Vec<T>::unpack(ld_vec_sys(own + (size_t)v * 16), acc);
+        else {
+#pragma unroll
+          for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+        }
+        int q = 0;
+        for (; q + 4 <= nsrc; q += 4) {
+          uint4 r[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) r[u] = ld_vec_sys((const char*)P.comm.buf[op->src[q + u]] + byte0 + (size_t)v * 16);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float f[N];
+            Vec<T>::unpack(r[u], f);
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[i] += f[i];
+          }
+        }
+        for (; q < nsrc; ++q) {
+          float f[N];
+          Vec<T>::unpack(ld_vec_sys((const char*)P.comm.buf[op->src[q]] + byte0 + (size_t)v * 16), f);
+#pragma unroll
+          for (int i = 0; i < N; ++i) acc[i] += f[i];
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] *= scale;
+        st_vec(own + (size_t)v * 16, Vec<T>::pack(acc));
+      }
+    }
+  }
+  if (tid == 0 && (it.nelem % N)) scalar_elems<T>(P, op, it.elem0 + (uint64_t)nvec * N, it.nelem % N);
+}
+
+// Entry and exit protocol shared by both paths.  Returns the wait context.
+__device__ __forceinline__ WaitCtx enter_collective(const SarLaunchParams& P, uint32_t block) {
+  WaitCtx w;
+  if (P.delay_ns) {
+    if (threadIdx.x == 0) {
+      const uint64_t t0 = globaltimer();
+      const uint64_t d = P.delay_ns < 10000000000ull ? P.delay_ns : 10000000000ull;
+      while (globaltimer() - t0 < d) __nanosleep(200);
+    }
+    __syncthreads();
+  }
+  w.deadline = globaltimer() + P.timeout_ns;
+  w.abort_flag = &P.comm.ctrl[P.rank]->abort_flag;
+  w.status = P.status;
+  if (block == 0 && threadIdx.x == 0) {
+    if (P.trace) P.trace[0] = globaltimer();
+    st_release_sys(&P.comm.ctrl[P.rank]->arrival, P.epoch_base);
+  }
+  return w;
+}
+
+// Called by one thread per block after all of the block's stores are ordered
+// before it (bar.sync).  The last block to finish announces the rank's exit and
+// waits until every participant has left: only then may the caller's next
+// kernel overwrite memory that peers were reading.
+__device__ void leave_collective(const SarLaunchParams& P, const WaitCtx& w, uint32_t nblocks) {
+  __threadfence();
+  SarCtrl* me = P.comm.ctrl[P.rank];
+  const uint32_t done = atomicAdd(&me->blocks_done, 1u) + 1u;
+  if (done != nblocks) return;
+  me->blocks_done = 0;
+  __threadfence();
+  if (*(volatile uint32_t*)w.abort_flag == 0) {
+    fence_sys();
+    st_release_sys(&me->exited, P.epoch_base);
+    for (int r = 0; r < P.nranks; ++r) {
+      if (r == P.rank || !(P.participants >> r & 1)) continue;
+      if (!wait_word(&P.comm.ctrl[r]->exited, P.epoch_base, w, SAR_TIMEOUT_EXIT)) break;
+    }
+  } else if (P.status) {
+    atomicCAS(P.status, 0u, (uint32_t)SAR_ABORTED);
+  }
+  if (P.trace) P.trace[1] = globaltimer();
+}
+
+template <typename T>
+__device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t nblocks) {
+  __shared__ Item s_item;
+  __shared__ int s_state;   // 1: item ready, 0: table exhausted, -1: a wait failed
+  WaitCtx w = enter_collective(P, block);
+  ItemWalker walk;
+  uint32_t arrived = 1u << P.rank;
+  if (threadIdx.x == 0) walk.init(&P, block, nblocks);
+  while (true) {
+    if (threadIdx.x == 0) {
+      Item it;
+      if (!walk.next(&it)) s_state = 0;
+      else if (!wait_item_ready(P, it, w, &arrived)) s_state = -1;
+      else { s_item = it; s_state = 1; }
+    }
+    __syncthreads();
+    if (s_state != 1) break;
+    const Item it = s_item;
+    simt_tile<T, 4>(P, it);
+    __syncthreads();   // every store of the tile is issued; s_item may be rewritten
+    if (threadIdx.x == 0) {
+      fence_sys();
+      publish_item(P, it.op, it.fidx);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) leave_collective(P, w, nblocks);
+}
+
+// -------------------------------------------------------------------- tma path
+namespace tma {
+constexpr int kStages = 6;
+constexpr int kStageBytes = 32768;
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = 32 * (1 + kConsumerWarps);
+constexpr int kPendingFlags = 8;
+
+struct StageDesc {
+  const SarOp* op;      // nullptr: no more work
+  uint64_t byte_off;    // offset of this piece in the buffers
+  uint32_t bytes;       // bytes per source in this piece (multiple of 16)
+  uint32_t slot_bytes;  // distance between sources inside the stage
+  uint32_t nsrc_total;  // buffers loaded into the stage (peers, then the own one if read)
+  uint32_t last;        // last piece of its item
+  uint32_t fidx;
+  uint32_t tail_elems;  // sub-vector tail of the item (handled with plain loads), last piece only
+  uint64_t tail_elem0;
+};
+
+struct Shared {
+  alignas(128) unsigned char ring[kStages][kStageBytes];
+  alignas(8) uint64_t full[kStages];
+  alignas(8) uint64_t empty[kStages];
+  StageDesc desc[kStages];
+  int abort_seen;
+  uint32_t issued;      // pieces the producer has issued (written when it stops)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait on a pipeline barrier
+__device__ __noinline__ bool mbar_wait(uint64_t* b, uint32_t parity, const WaitCtx& w) {
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(b, parity)) return true;
+    if ((it & 63) == 63) {
+      if (*(volatile uint32_t*)w.abort_flag) return false;
+      if (globaltimer() > w.deadline) { record_failure(w, SAR_TIMEOUT_PIPE); return false; }
+    }
+  }
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps) : "memory"); }
+
+__device__ __forceinline__ uint32_t pow2_ceil(uint32_t x) {
+  uint32_t p = 1;
+  while (p < x) p <<= 1;
+  return p;
+}
+}  // namespace tma
+
+template <typename T>
+__device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t nblocks, tma::Shared& S) {
+  using namespace tma;
+  constexpr int N = Vec<T>::N;
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5, lane = tid & 31;
+  WaitCtx w = enter_collective(P, block);
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    S.abort_seen = 0;
+    S.issued = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      ItemWalker walk;
+      walk.init(&P, block, nblocks);
+      uint32_t arrived = 1u << P.rank;
+      uint32_t seq = 0;           // pieces issued
+      bool ok = true;
+      Item it;
+      auto acquire_stage = [&](uint32_t s) -> bool {
+        // the first pass over the ring finds every stage free
+        if (seq >= (uint32_t)kStages) return mbar_wait(&S.empty[s], ((seq / kStages) - 1) & 1, w);
+        return true;
+      };
+      while (ok && walk.next(&it)) {
+        if (!wait_item_ready(P, it, w, &arrived)) { ok = false; break; }
+        fence_proxy_async();   // flags were acquired through the generic proxy; the copies below use the async one
+        const SarOp* op = it.op;
+        const bool local = op_reads_local(op);
+        const uint32_t nsrc_total = op->nsrc + (local ? 1u : 0u);
+        const uint32_t slot_bytes = kStageBytes / pow2_ceil(nsrc_total);
+        const uint32_t vec_bytes = (it.nelem / N) * 16u;
+        const uint32_t tail = it.nelem % N;
+        uint32_t done = 0;
+        do {
+          const uint32_t bytes = vec_bytes - done < slot_bytes ? vec_bytes - done : slot_bytes;
+          const uint32_t s = seq % kStages;
+          if (!acquire_stage(s)) { ok = false; break; }
+          StageDesc& d = S.desc[s];
+          d.op = op; d.byte_off = it.elem0 * sizeof(T) + done; d.bytes = bytes; d.slot_bytes = slot_bytes;
+          d.nsrc_total = nsrc_total; d.fidx = it.fidx;
+          d.last = (done + bytes >= vec_bytes) ? 1u : 0u;
+          d.tail_elems = d.last ? tail : 0u;
+          d.tail_elem0 = it.elem0 + (uint64_t)(it.nelem / N) * N;
+          if (bytes) {
+            mbar_arrive_expect_tx(&S.full[s], bytes * nsrc_total);
+            for (uint32_t q = 0; q < op->nsrc; ++q)
+              bulk_load(&S.ring[s][q * slot_bytes], (const char*)P.comm.buf[op->src[q]] + d.byte_off, bytes, &S.full[s]);
+            if (local)
+              bulk_load(&S.ring[s][op->nsrc * slot_bytes], (const char*)P.comm.buf[P.rank] + d.byte_off, bytes, &S.full[s]);
+          } else {
+            mbar_arrive(&S.full[s]);   // an item that is only a sub-vector tail
+          }
+          ++seq;
+          done += bytes;
+        } while (done < vec_bytes);
+      }
+      // end marker (also after a failure, so that the consumers stop)
+      {
+        const uint32_t s = seq % kStages;
+        bool got = true;
+        if (seq >= (uint32_t)kStages) {
+          // on the failure path the deadline has usually passed: take the stage only if it is free already
+          got = ok ? mbar_wait(&S.empty[s], ((seq / kStages) - 1) & 1, w) : mbar_try_wait(&S.empty[s], ((seq / kStages) - 1) & 1);
+        }
+        if (got) { S.desc[s].op = nullptr; mbar_arrive(&S.full[s]); }
+        else *(volatile int*)&S.abort_seen = 1;
+      }
+      S.issued = seq;
+    }
+  } else {
+    // --------------------------------------------------------------- consumers
+    const uint32_t ctid = tid - 32;                 // 0 .. 127
+    constexpr uint32_t CT = 32 * kConsumerWarps;
+    uint32_t seq = 0;
+    // flags are published two store groups late, so that their data has landed
+    uint32_t pend_fidx[kPendingFlags];
+    const SarOp* pend_op[kPendingFlags];
+    uint32_t pend_seq[kPendingFlags] = {};
+    uint32_t pend_head = 0, pend_tail = 0;
+    auto flush_flags = [&](uint32_t complete_upto) {   // store groups with seq < complete_upto have landed
+      bool any = false;
+      while (pend_head != pend_tail && pend_seq[pend_head % kPendingFlags] < complete_upto) {
+        if (!any) { fence_proxy_async(); fence_sys(); any = true; }
+        publish_item(P, pend_op[pend_head % kPendingFlags], pend_fidx[pend_head % kPendingFlags]);
+        ++pend_head;
+      }
+    };
+    while (true) {
+      const uint32_t s = seq % kStages;
+      bool ok = true;
+      if (lane == 0) {
+        if (ctid == 0 && pend_head != pend_tail && !mbar_try_wait(&S.full[s], (seq / kStages) & 1)) {
+          // The pipeline has run dry, perhaps because the producer waits for a
+          // tile that (through other ranks) depends on an item still held back
+          // here: announce everything now.
+          bulk_wait_all<0>();
+          flush_flags(0xffffffffu);
+        }
+        ok = mbar_wait(&S.full[s], (seq / kStages) & 1, w);
+        if (*(volatile int*)&S.abort_seen) ok = false;
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      const StageDesc d = S.desc[s];
+      if (d.op == nullptr) break;
+      const SarOp* op = d.op;
+      unsigned char* stage = S.ring[s];
+      if (op->kind != SAR_COPY && d.bytes) {
+        const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
+        const uint32_t nvec = d.bytes / 16;
+        for (uint32_t v = ctid; v < nvec; v += CT) {
+          float acc[N];
+          Vec<T>::unpack(*reinterpret_cast<const uint4*>(stage + (size_t)v * 16), acc);
+          for (uint32_t q = 1; q < d.nsrc_total; ++q) {
+            float f[N];
+            Vec<T>::unpack(*reinterpret_cast<const uint4*>(stage + (size_t)q * d.slot_bytes + (size_t)v * 16), f);
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[i] += f[i];
+          }
+#pragma unroll
+          for (int i = 0; i < N; ++i) acc[i] *= scale;
+          *reinterpret_cast<uint4*>(stage + (size_t)v * 16) = Vec<T>::pack(acc);
+        }
+        fence_proxy_async();   // make the sums visible to the bulk store engine
+      }
+      // Every consumer warp is done with this piece's descriptor and data, and
+      // (a fortiori) with the previous piece's stage, which is released below.
+      consumer_bar();
+      if (ctid == 0) {
+        if (d.bytes) {
+          fence_proxy_async();
+          bulk_store((char*)P.comm.buf[P.rank] + d.byte_off, stage, d.bytes);
+          if (op->kind == SAR_REDUCE_PUSH) bulk_store((char*)P.comm.buf[op->src[0]] + d.byte_off, stage, d.bytes);
+        }
+        bulk_commit();          // one group per piece (possibly empty), so group numbers follow seq
+        if (d.last) {
+          if (d.tail_elems) scalar_elems<T>(P, op, d.tail_elem0, d.tail_elems);
+          pend_op[pend_tail % kPendingFlags] = op;
+          pend_fidx[pend_tail % kPendingFlags] = d.fidx;
+          pend_seq[pend_tail % kPendingFlags] = seq;
+          ++pend_tail;
+        }
+        // the previous piece's stores have read their stage: hand it back
+        bulk_wait_read<1>();
+        if (seq >= 1) mbar_arrive(&S.empty[(seq - 1) % kStages]);
+        // An item is announced once its last store group has landed.  Waiting for
+        // that right away would stall this thread for a store round trip per item,
+        // so the wait is taken two pieces late, and only if an item is due.
+        if (pend_head != pend_tail && pend_seq[pend_head % kPendingFlags] + 2 <= seq) {
+          bulk_wait_all<2>();          // groups up to seq-2 are complete
+          flush_flags(seq - 1);
+        }
+        if (pend_tail - pend_head >= (uint32_t)kPendingFlags - 1) { bulk_wait_all<0>(); flush_flags(seq + 1); }
+      }
+      ++seq;
+    }
+    if (ctid == 0) {
+      bulk_wait_all<0>();
+      flush_flags(0xffffffffu);
+    }
+  }
+  __syncthreads();
+  // Bulk loads still in flight would write into shared memory after the block
+  // has gone.  On the failure path the consumers may not have waited for every
+  // issued piece: wait here (at most 2 ms) for the newest use of every stage.
+  if (tid == 0 && *(volatile uint32_t*)w.abort_flag) {
+    const uint32_t issued = S.issued;
+    const uint64_t limit = globaltimer() + 2000000ull;
+    for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+      if (issued <= s) continue;
+      const uint32_t use = (issued - 1 - s) / kStages;   // newest use of stage s
+      while (!mbar_try_wait(&S.full[s], use & 1) && globaltimer() < limit) {}
+    }
+  }
+  __syncthreads();
+  if (tid == 0) leave_collective(P, w, nblocks);
+}
+
+}  // namespace sar_dev

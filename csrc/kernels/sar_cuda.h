@@ -1,0 +1,59 @@
+// Host interface of the CUDA kernels (C linkage; usable from C++, ctypes and
+// the torch extension).  All functions return a cudaError_t value as int
+// (0 = success) unless stated otherwise; they never allocate.
+#pragma once
+#include <stdint.h>
+
+#include "../core/table.h"
+
+struct SarLaunchParams;
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum SarPath { SAR_PATH_SIMT = 0, SAR_PATH_TMA = 1 };
+
+// blocks <= 0 picks the default for the path.  threads is used by the simt
+// path only (<= 0: 512).
+int sar_cuda_launch(const struct SarLaunchParams* p, int path, int blocks, int threads, void* stream);
+// n ranks emulated on the current device by ONE cooperative launch: d_params
+// points to n SarLaunchParams in device memory; rank r is run by blocks
+// [r*blocks_per_rank, (r+1)*blocks_per_rank).  Fails with
+// cudaErrorCooperativeLaunchTooLarge when the blocks cannot all be resident.
+int sar_cuda_launch_emulated(const struct SarLaunchParams* d_params, int n, int dtype, int path, int blocks_per_rank,
+                             int threads, void* stream);
+int sar_cuda_default_blocks(int path);
+int sar_cuda_max_emulated_blocks(int dtype, int path, int threads);   // resident blocks on the current device
+
+// Barrier across ranks on control channel `channel`: announces `epoch` and
+// waits (bounded) until every rank in `participants` has announced it.
+int sar_cuda_barrier(SarCtrl* const* ctrl /*host array of nranks device ptrs*/, int rank, int nranks,
+                     uint32_t participants, uint32_t epoch, uint64_t timeout_ns, uint32_t* status, void* stream);
+
+// Busy-wait on the device for `ns` nanoseconds of %globaltimer (at most 10 s):
+// the injected straggler delay (cf. gpu_sleep_kernel, stragglar/allreduce_8GPU.cu:36-39,
+// which counts SM clocks and so depends on the clock the GPU happens to run at).
+int sar_cuda_delay(uint64_t ns, void* stream);
+// dst[i] = uniform[-1, 1) from a counter hash of (seed, i); same values as sar_host_uniform.
+int sar_cuda_fill_uniform(void* dst, uint64_t count, int dtype, uint64_t seed, void* stream);
+// dst[i] = (T)(sum over r of (float)(T)uniform(seeds[r], i)) for i in [begin, end): what a
+// reduce-scatter over inputs made by sar_cuda_fill_uniform leaves in a chunk (fp32
+// accumulation, one rounding).  Used to emulate a finished pre-phase.
+int sar_cuda_fill_uniform_sum(void* dst, uint64_t begin, uint64_t end, int dtype, const uint64_t* seeds, int nseeds,
+                              void* stream);
+int sar_cuda_fill_const(void* dst, uint64_t count, int dtype, float value, void* stream);
+// dst[i] = (dst_dtype)(src[i] * scale); src and dst may alias when the dtypes agree.
+int sar_cuda_scale_cast(void* dst, int dst_dtype, const void* src, int src_dtype, uint64_t count, float scale,
+                        void* stream);
+// Checks buf[i] against scale * sum over r of uniform(seeds[r], i) for i in
+// [begin, end); result[0] = number of elements off by more than
+// atol + rtol*|want|, result[1] = max abs error as float bits.  result is
+// device memory (2 x uint32) and is zeroed by the call.
+int sar_cuda_verify_uniform_sum(const void* buf, uint64_t begin, uint64_t end, int dtype, const uint64_t* seeds,
+                                int nseeds, float scale, float atol, float rtol, uint32_t* result, void* stream);
+float sar_host_uniform(uint64_t seed, uint64_t index);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,30 @@
+// Launch parameters of the table-executing kernels (plain data, shared by
+// host and device code).
+#pragma once
+#include <stdint.h>
+
+#include "../core/table.h"
+
+struct SarDevComm {
+  uint32_t* flags[SAR_MAX_RANKS];  // this collective's channel of every rank's flag array
+  SarCtrl* ctrl[SAR_MAX_RANKS];    // this collective's channel of every rank's control words
+  void* buf[SAR_MAX_RANKS];        // every rank's data buffer (same layout)
+};
+
+struct SarLaunchParams {
+  SarDevComm comm;
+  const SarOp* ops;
+  const uint16_t* round_begin;  // num_rounds + 1 entries
+  uint32_t num_rounds;
+  SarGeom geom;
+  int32_t rank, nranks;
+  uint32_t participants;
+  uint32_t epoch_base;
+  float scale;
+  int32_t dtype;
+  uint64_t timeout_ns;
+  uint32_t* status;       // first failure of this launch (0 = ok); may be mapped host memory
+  uint64_t* trace;        // optional: [0] = arrival time, [1] = end time (%globaltimer ns), else nullptr
+  uint64_t delay_ns;      // spin this long before arriving (a late rank when ranks share one launch)
+};
+

@@ -1,0 +1,267 @@
+#include "local_comm.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../core/host_exec.h"
+#include "../kernels/sar_params.h"
+#include "../kernels/sar_cuda.h"
+
+namespace {
+struct DevTable { SarOp* ops = nullptr; uint16_t* round_begin = nullptr; uint32_t num_rounds = 0; };
+struct Rank {
+  int dev = 0;
+  cudaStream_t stream = nullptr;
+  uint32_t* flags = nullptr;   // SAR_NUM_CHANNELS * SAR_FLAG_CAPACITY
+  SarCtrl* ctrl = nullptr;     // SAR_NUM_CHANNELS
+  uint32_t* status = nullptr;  // 1 word
+  uint64_t* trace = nullptr;   // 2 words
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  bool timed = false;
+  std::map<std::pair<const void*, int>, DevTable> tables;
+};
+}  // namespace
+
+struct sar_local_comm {
+  int n = 0;
+  bool emulate = false;
+  std::vector<Rank> ranks;
+  uint32_t epoch[SAR_NUM_CHANNELS] = {};
+  SarLaunchParams* d_params = nullptr;   // emulate: n entries on devices[0]
+};
+
+#define CK(x)                                                                          \
+  do {                                                                                 \
+    cudaError_t e_ = (x);                                                              \
+    if (e_ != cudaSuccess) {                                                           \
+      if (err && errlen > 0) snprintf(err, errlen, "%s: %s", #x, cudaGetErrorString(e_)); \
+      return fail_value;                                                               \
+    }                                                                                  \
+  } while (0)
+
+static DevTable* upload(Rank& rk, const sar_table* t, int rank, char* err, int errlen) {
+  auto key = std::make_pair((const void*)t, rank);
+  auto it = rk.tables.find(key);
+  if (it != rk.tables.end()) return &it->second;
+  DevTable* fail_value = nullptr;
+  DevTable d;
+  const int nops = sar_table_num_ops(t, rank);
+  const int nrb = sar_table_num_round_begin(t, rank);
+  CK(cudaMalloc(&d.ops, sizeof(SarOp) * (nops > 0 ? nops : 1)));
+  CK(cudaMalloc(&d.round_begin, sizeof(uint16_t) * (nrb > 0 ? nrb : 1)));
+  if (nops) CK(cudaMemcpy(d.ops, sar_table_ops(t, rank), sizeof(SarOp) * nops, cudaMemcpyHostToDevice));
+  if (nrb) CK(cudaMemcpy(d.round_begin, sar_table_round_begin(t, rank), sizeof(uint16_t) * nrb, cudaMemcpyHostToDevice));
+  d.num_rounds = nrb > 0 ? (uint32_t)(nrb - 1) : 0;
+  return &(rk.tables[key] = d);
+}
+
+extern "C" {
+
+sar_local_comm* sar_local_create(int n, const int* devices, int emulate, char* err, int errlen) {
+  sar_local_comm* fail_value = nullptr;
+  if (n < 1 || n > SAR_MAX_RANKS) {
+    if (err) snprintf(err, errlen, "rank count %d out of range", n);
+    return nullptr;
+  }
+  auto* c = new sar_local_comm;
+  c->n = n; c->emulate = emulate != 0;
+  c->ranks.resize(n);
+  for (int r = 0; r < n; ++r) {
+    Rank& rk = c->ranks[r];
+    rk.dev = emulate ? devices[0] : devices[r];
+    CK(cudaSetDevice(rk.dev));
+    if (emulate && r > 0) rk.stream = c->ranks[0].stream;
+    else CK(cudaStreamCreateWithFlags(&rk.stream, cudaStreamNonBlocking));
+    const size_t fbytes = sizeof(uint32_t) * SAR_NUM_CHANNELS * (size_t)SAR_FLAG_CAPACITY;
+    CK(cudaMalloc(&rk.flags, fbytes));
+    CK(cudaMemset(rk.flags, 0, fbytes));
+    CK(cudaMalloc(&rk.ctrl, sizeof(SarCtrl) * SAR_NUM_CHANNELS));
+    CK(cudaMemset(rk.ctrl, 0, sizeof(SarCtrl) * SAR_NUM_CHANNELS));
+    CK(cudaMalloc(&rk.status, 16));
+    CK(cudaMemset(rk.status, 0, 16));
+    CK(cudaMalloc(&rk.trace, 16));
+    CK(cudaMemset(rk.trace, 0, 16));
+    CK(cudaEventCreate(&rk.ev0));
+    CK(cudaEventCreate(&rk.ev1));
+  }
+  if (emulate) {
+    CK(cudaSetDevice(devices[0]));
+    CK(cudaMalloc(&c->d_params, sizeof(SarLaunchParams) * n));
+  } else {
+    for (int a = 0; a < n; ++a) {
+      CK(cudaSetDevice(c->ranks[a].dev));
+      for (int b = 0; b < n; ++b) {
+        if (a == b || c->ranks[a].dev == c->ranks[b].dev) continue;
+        int can = 0;
+        CK(cudaDeviceCanAccessPeer(&can, c->ranks[a].dev, c->ranks[b].dev));
+        if (!can) {
+          if (err) snprintf(err, errlen, "device %d cannot access device %d", c->ranks[a].dev, c->ranks[b].dev);
+          return nullptr;
+        }
+        cudaError_t e = cudaDeviceEnablePeerAccess(c->ranks[b].dev, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+        else CK(e);
+      }
+    }
+  }
+  for (int r = 0; r < n; ++r) { CK(cudaSetDevice(c->ranks[r].dev)); CK(cudaDeviceSynchronize()); }
+  return c;
+}
+
+void sar_local_destroy(sar_local_comm* c) {
+  if (!c) return;
+  for (int r = 0; r < c->n; ++r) {
+    Rank& rk = c->ranks[r];
+    cudaSetDevice(rk.dev);
+    cudaDeviceSynchronize();
+    for (auto& kv : rk.tables) { cudaFree(kv.second.ops); cudaFree(kv.second.round_begin); }
+    cudaFree(rk.flags); cudaFree(rk.ctrl); cudaFree(rk.status); cudaFree(rk.trace);
+    cudaEventDestroy(rk.ev0); cudaEventDestroy(rk.ev1);
+    if (!(c->emulate && r > 0)) cudaStreamDestroy(rk.stream);
+  }
+  if (c->d_params) { cudaSetDevice(c->ranks[0].dev); cudaFree(c->d_params); }
+  delete c;
+}
+
+int sar_local_nranks(const sar_local_comm* c) { return c->n; }
+void* sar_local_stream(sar_local_comm* c, int rank) { return c->ranks[rank].stream; }
+
+int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs, uint64_t count, int dtype,
+                  const sar_run_opts* o, const uint64_t* delay_ns, char* err, int errlen) {
+  int fail_value = 1;
+  const int n = c->n;
+  const int nph = sar_program_num_phases(prog);
+  if (nph < 1 || sar_table_nranks(sar_program_phase(prog, 0)) != n) {
+    if (err) snprintf(err, errlen, "program is for %d ranks, communicator has %d", nph ? sar_table_nranks(sar_program_phase(prog, 0)) : 0, n);
+    return 1;
+  }
+  for (int r = 0; r < n; ++r)
+    if (((uintptr_t)bufs[r]) & 15) { if (err) snprintf(err, errlen, "buffer of rank %d is not 16-byte aligned", r); return 1; }
+  const uint32_t esize = dtype == SAR_F32 ? 4 : 2;
+  const int path = o->path;
+  int blocks = o->blocks > 0 ? o->blocks : sar_cuda_default_blocks(path);
+  const double timeout_s = o->timeout_s > 0 ? o->timeout_s : 10.0;
+  const uint32_t tile_max = o->tile_bytes ? o->tile_bytes : (128u << 10);
+  std::vector<bool> delayed(n, false);
+
+  if (o->timed) {
+    // device-side start barrier on the last channel, then the start event
+    const uint32_t ep = ++c->epoch[SAR_NUM_CHANNELS - 1];
+    if (!c->emulate) {
+      SarCtrl* ctrl[SAR_MAX_RANKS];
+      for (int r = 0; r < n; ++r) ctrl[r] = c->ranks[r].ctrl + (SAR_NUM_CHANNELS - 1);
+      for (int r = 0; r < n; ++r) {
+        CK(cudaSetDevice(c->ranks[r].dev));
+        CK((cudaError_t)sar_cuda_barrier(ctrl, r, n, (1u << n) - 1u, ep, (uint64_t)(timeout_s * 1e9), c->ranks[r].status, c->ranks[r].stream));
+      }
+    }
+    for (int r = 0; r < n; ++r) {
+      if (c->emulate && r > 0) break;
+      CK(cudaSetDevice(c->ranks[r].dev));
+      CK(cudaEventRecord(c->ranks[r].ev0, c->ranks[r].stream));
+    }
+  }
+  for (int r = 0; r < n; ++r) c->ranks[r].timed = o->timed != 0;
+
+  for (int ph = 0; ph < nph; ++ph) {
+    const sar_table* t = sar_program_phase(prog, ph);
+    const int ch = sar_table_channel(t);
+    const uint32_t parts = sar_table_participants(t);
+    const uint32_t nch = (uint32_t)sar_table_num_chunks(t);
+    c->epoch[ch] += SAR_VER_STRIDE;
+    const uint32_t tile_elems = sar_pick_tile_elems(count, esize, nch, (uint32_t)blocks, 2048, tile_max);
+    SarGeom g = sar::make_geom(count, esize, nch, tile_elems);
+    if ((uint64_t)g.tiles_per_chunk * g.num_chunks > SAR_FLAG_CAPACITY) {
+      if (err) snprintf(err, errlen, "buffer too large for the flag array");
+      return 1;
+    }
+    std::vector<SarLaunchParams> hp(n);
+    for (int r = 0; r < n; ++r) {
+      Rank& rk = c->ranks[r];
+      SarLaunchParams& P = hp[r];
+      memset(&P, 0, sizeof(P));
+      for (int q = 0; q < n; ++q) {
+        P.comm.flags[q] = c->ranks[q].flags + (size_t)ch * SAR_FLAG_CAPACITY;
+        P.comm.ctrl[q] = c->ranks[q].ctrl + ch;
+        P.comm.buf[q] = bufs[q];
+      }
+      CK(cudaSetDevice(rk.dev));
+      DevTable* dt = upload(rk, t, r, err, errlen);
+      if (!dt) return 1;
+      P.ops = dt->ops; P.round_begin = dt->round_begin; P.num_rounds = dt->num_rounds;
+      P.geom = g; P.rank = r; P.nranks = n; P.participants = parts;
+      P.epoch_base = c->epoch[ch]; P.scale = o->scale; P.dtype = dtype;
+      P.timeout_ns = (uint64_t)(timeout_s * 1e9);
+      P.status = rk.status; P.trace = rk.trace;
+      P.delay_ns = 0;
+      if (c->emulate && delay_ns && delay_ns[r] && !delayed[r] && (parts >> r & 1)) { P.delay_ns = delay_ns[r]; delayed[r] = true; }
+    }
+    if (c->emulate) {
+      CK(cudaSetDevice(c->ranks[0].dev));
+      CK(cudaMemcpyAsync(c->d_params, hp.data(), sizeof(SarLaunchParams) * n, cudaMemcpyHostToDevice, c->ranks[0].stream));
+      // the copy is from pageable memory: it has completed with respect to the host buffer on return
+      cudaError_t e = (cudaError_t)sar_cuda_launch_emulated(c->d_params, n, dtype, path, blocks, o->threads, c->ranks[0].stream);
+      if (e != cudaSuccess) {
+        if (err) snprintf(err, errlen, "emulated launch (%d ranks x %d blocks): %s", n, blocks, cudaGetErrorString(e));
+        return (int)e;
+      }
+    } else {
+      for (int r = 0; r < n; ++r) {
+        if (!(parts >> r & 1)) continue;
+        Rank& rk = c->ranks[r];
+        CK(cudaSetDevice(rk.dev));
+        if (delay_ns && delay_ns[r] && !delayed[r]) { CK((cudaError_t)sar_cuda_delay(delay_ns[r], rk.stream)); delayed[r] = true; }
+        CK((cudaError_t)sar_cuda_launch(&hp[r], path, blocks, o->threads, rk.stream));
+      }
+    }
+  }
+  if (o->timed) {
+    for (int r = 0; r < n; ++r) {
+      if (c->emulate && r > 0) break;
+      CK(cudaSetDevice(c->ranks[r].dev));
+      CK(cudaEventRecord(c->ranks[r].ev1, c->ranks[r].stream));
+    }
+  }
+  return 0;
+}
+
+uint32_t sar_local_sync(sar_local_comm* c, float* ms) {
+  uint32_t worst = 0;
+  for (int r = 0; r < c->n; ++r) {
+    Rank& rk = c->ranks[r];
+    cudaSetDevice(rk.dev);
+    cudaError_t e = cudaStreamSynchronize(rk.stream);
+    if (e != cudaSuccess) { worst = 0x1000u + (uint32_t)e; continue; }
+    uint32_t st = 0;
+    cudaMemcpy(&st, rk.status, 4, cudaMemcpyDeviceToHost);
+    if (st) {
+      worst = worst > st ? worst : st;
+      cudaMemset(rk.status, 0, 4);
+      for (int ch = 0; ch < SAR_NUM_CHANNELS; ++ch) {
+        cudaMemset(&rk.ctrl[ch].abort_flag, 0, 4);
+        cudaMemset(&rk.ctrl[ch].blocks_done, 0, 4);
+      }
+    }
+    if (ms) {
+      ms[r] = 0.f;
+      const Rank& ev = c->emulate ? c->ranks[0] : rk;
+      if (rk.timed) cudaEventElapsedTime(&ms[r], ev.ev0, ev.ev1);
+    }
+  }
+  return worst;
+}
+
+int sar_local_trace(sar_local_comm* c, uint64_t* out) {
+  for (int r = 0; r < c->n; ++r) {
+    cudaSetDevice(c->ranks[r].dev);
+    cudaError_t e = cudaMemcpy(out + 2 * r, c->ranks[r].trace, 16, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+}
