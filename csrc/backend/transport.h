@@ -1,0 +1,76 @@
+// Symmetric arenas of a process group, as one rank sees them.
+//
+// Every rank owns one region with the same layout:
+//   [control words | status | flags (all channels) | data]
+// and maps every peer's region into its own address space: CUDA IPC handles
+// for device memory, POSIX shared memory for host memory.  The handles (or
+// names) travel through the c10d Store the process group was given; the
+// reference backend instead opened its own TCP socket on a fixed port and
+// ignored the Store (implementation/custom_backend/src/dummy.cpp:170-211,813-819).
+#pragma once
+#include <c10/util/intrusive_ptr.h>
+#include <torch/csrc/distributed/c10d/Store.hpp>
+
+#include <atomic>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../core/table.h"
+
+namespace sarpg {
+
+struct ArenaLayout {
+  static constexpr size_t kCtrlOff = 0;
+  static constexpr size_t kStatusOff = 2048;
+  static constexpr size_t kFlagsOff = 4096;
+  static constexpr size_t kFlagsBytes = sizeof(uint32_t) * (size_t)SAR_NUM_CHANNELS * SAR_FLAG_CAPACITY;
+  static constexpr size_t kDataOff = kFlagsOff + kFlagsBytes;
+};
+
+class Transport {
+ public:
+  Transport(bool cuda, int device, int rank, int n, size_t data_bytes, size_t staging_bytes,
+            const c10::intrusive_ptr<c10d::Store>& store, const std::string& key_prefix);
+  ~Transport();
+  Transport(const Transport&) = delete;
+
+  bool cuda() const { return cuda_; }
+  int device() const { return device_; }
+  int rank() const { return rank_; }
+  int size() const { return n_; }
+  char* base(int r) const { return base_[r]; }
+  char* data(int r) const { return base_[r] + ArenaLayout::kDataOff; }
+  uint32_t* flags(int r, int channel) const {
+    return reinterpret_cast<uint32_t*>(base_[r] + ArenaLayout::kFlagsOff) + (size_t)channel * SAR_FLAG_CAPACITY;
+  }
+  SarCtrl* ctrl(int r, int channel) const { return reinterpret_cast<SarCtrl*>(base_[r] + ArenaLayout::kCtrlOff) + channel; }
+  uint32_t* status() const { return reinterpret_cast<uint32_t*>(base_[rank_] + ArenaLayout::kStatusOff); }
+  size_t data_bytes() const { return data_bytes_; }
+  size_t staging_bytes() const { return staging_bytes_; }
+  size_t staging_off() const { return data_bytes_ - staging_bytes_; }   // staging sits at the end of the data region
+  size_t heap_bytes() const { return data_bytes_ - staging_bytes_; }
+
+  // next epoch base of a channel (every rank calls this in the same order)
+  uint32_t next_epoch(int channel) { return epoch_[channel] += SAR_VER_STRIDE; }
+  uint32_t next_barrier_epoch() { return ++barrier_epoch_; }
+
+  // offset into the data region if p lies inside this rank's heap, else -1
+  int64_t heap_offset(const void* p, size_t bytes) const;
+  // symmetric heap: the same call sequence on every rank yields the same offsets
+  int64_t heap_alloc(size_t bytes);
+  void heap_free(int64_t off);
+
+ private:
+  bool cuda_;
+  int device_, rank_, n_;
+  size_t data_bytes_, staging_bytes_, total_bytes_;
+  char* base_[SAR_MAX_RANKS] = {};
+  uint32_t epoch_[SAR_NUM_CHANNELS] = {};
+  uint32_t barrier_epoch_ = 0;
+  std::string shm_name_;
+  struct Block { size_t off, bytes; bool used; };
+  std::vector<Block> blocks_;
+};
+
+}  // namespace sarpg

@@ -60,6 +60,19 @@ __global__ void sar_barrier_kernel(SarDevComm comm, int rank, int nranks, uint32
   }
 }
 
+__global__ void sar_signal_wait_kernel(uint32_t* set_ptr, uint32_t set_val, const uint32_t* wait_ptr, uint32_t wait_val,
+                                       uint64_t timeout_ns, uint32_t* abort_flag, uint32_t* status) {
+  if (threadIdx.x != 0) return;
+  if (set_ptr) { fence_sys(); st_release_sys(set_ptr, set_val); }
+  if (wait_ptr) {
+    WaitCtx w;
+    w.deadline = globaltimer() + timeout_ns;
+    w.abort_flag = abort_flag;
+    w.status = status;
+    wait_word(wait_ptr, wait_val, w, SAR_TIMEOUT_FLAG);
+  }
+}
+
 __global__ void sar_delay_kernel(uint64_t ns) {
   const uint64_t t0 = globaltimer();
   while (globaltimer() - t0 < ns) __nanosleep(200);
@@ -135,6 +148,32 @@ __global__ void sar_fill_uniform_sum_kernel(T* dst, uint64_t begin, uint64_t end
     float acc = 0.f;
     for (int r = 0; r < seeds.n; ++r) acc += to_float(from_float<T>(sar_uniform(seeds.s[r], i)));
     dst[i] = from_float<T>(acc);
+  }
+}
+
+struct SegList { SarCopySeg s[SAR_MAX_RANKS]; int n; };
+__global__ void sar_copy_segments_kernel(SegList L) {
+  for (int k = 0; k < L.n; ++k) {
+    const char* src = (const char*)L.s[k].src;
+    char* dst = (char*)L.s[k].dst;
+    const uint64_t bytes = L.s[k].bytes;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, t = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+      const uint64_t nvec = bytes / 16;
+      for (uint64_t i = t; i < nvec; i += stride) st_vec(dst + i * 16, ld_vec_sys(src + i * 16));
+      for (uint64_t i = nvec * 16 + t; i < bytes; i += stride) dst[i] = *(volatile const char*)(src + i);
+    } else {
+      for (uint64_t i = t; i < bytes; i += stride) dst[i] = *(volatile const char*)(src + i);
+    }
+  }
+}
+struct SrcList { const void* p[SAR_MAX_RANKS]; int n; };
+template <typename T>
+__global__ void sar_reduce_segments_kernel(T* dst, SrcList L, uint64_t count, float scale) {
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < L.n; ++k) acc += Vec<T>::load1((const char*)L.p[k] + i * sizeof(T));
+    dst[i] = from_float<T>(acc * scale);
   }
 }
 
@@ -295,6 +334,37 @@ int sar_cuda_verify_uniform_sum(const void* buf, uint64_t begin, uint64_t end, i
     sar_verify_kernel<T><<<grid_for(end - begin, 256), 256, 0, st>>>((const T*)buf, begin, end, sl, scale, atol, rtol, result);
     return (int)cudaGetLastError();
   });
+}
+
+int sar_cuda_copy_segments(const SarCopySeg* segs, int nseg, void* stream) {
+  if (nseg < 0 || nseg > SAR_MAX_RANKS) return (int)cudaErrorInvalidValue;
+  if (nseg == 0) return 0;
+  SegList L{};
+  L.n = nseg;
+  uint64_t mx = 0;
+  for (int i = 0; i < nseg; ++i) { L.s[i] = segs[i]; mx = segs[i].bytes > mx ? segs[i].bytes : mx; }
+  sar_copy_segments_kernel<<<grid_for(mx / 16 + 1, 256), 256, 0, (cudaStream_t)stream>>>(L);
+  return (int)cudaGetLastError();
+}
+
+int sar_cuda_reduce_segments(void* dst, const void* const* srcs, int nsrc, uint64_t count, int dtype, float scale,
+                             void* stream) {
+  if (nsrc < 1 || nsrc > SAR_MAX_RANKS) return (int)cudaErrorInvalidValue;
+  if (count == 0) return 0;
+  SrcList L{};
+  L.n = nsrc;
+  for (int i = 0; i < nsrc; ++i) L.p[i] = srcs[i];
+  return with_dtype(dtype, [&](auto tag) -> int {
+    using T = decltype(tag);
+    sar_reduce_segments_kernel<T><<<grid_for(count, 256), 256, 0, (cudaStream_t)stream>>>((T*)dst, L, count, scale);
+    return (int)cudaGetLastError();
+  });
+}
+
+int sar_cuda_signal_wait(uint32_t* set_ptr, uint32_t set_val, const uint32_t* wait_ptr, uint32_t wait_val,
+                         uint64_t timeout_ns, uint32_t* abort_flag, uint32_t* status, void* stream) {
+  sar_signal_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(set_ptr, set_val, wait_ptr, wait_val, timeout_ns, abort_flag, status);
+  return (int)cudaGetLastError();
 }
 
 float sar_host_uniform(uint64_t seed, uint64_t index) { return sar_uniform(seed, index); }

@@ -52,6 +52,19 @@ int sar_cuda_scale_cast(void* dst, int dst_dtype, const void* src, int src_dtype
 // device memory (2 x uint32) and is zeroed by the call.
 int sar_cuda_verify_uniform_sum(const void* buf, uint64_t begin, uint64_t end, int dtype, const uint64_t* seeds,
                                 int nseeds, float scale, float atol, float rtol, uint32_t* result, void* stream);
+// Plain data movement for the backend's staged collectives (broadcast,
+// all-gather, ...): up to SAR_MAX_RANKS segments per launch, each copied from
+// `src` (local or peer memory, read with system-scope loads) to local `dst`.
+struct SarCopySeg { const void* src; void* dst; uint64_t bytes; };
+int sar_cuda_copy_segments(const struct SarCopySeg* segs, int nseg, void* stream);
+// dst[i] = scale * sum over k of srcs[k][i]  (fp32 accumulation, one rounding)
+int sar_cuda_reduce_segments(void* dst, const void* const* srcs, int nsrc, uint64_t count, int dtype, float scale,
+                             void* stream);
+// One thread: release-store set_val to *set_ptr (if set_ptr), then wait
+// (bounded) until *wait_ptr has reached wait_val (if wait_ptr).  The building
+// block of the backend's point-to-point send/recv handshake.
+int sar_cuda_signal_wait(uint32_t* set_ptr, uint32_t set_val, const uint32_t* wait_ptr, uint32_t wait_val,
+                         uint64_t timeout_ns, uint32_t* abort_flag, uint32_t* status, void* stream);
 float sar_host_uniform(uint64_t seed, uint64_t index);
 
 #ifdef __cplusplus

@@ -1,0 +1,129 @@
+"""PyTorch integration: the ``stragglar`` c10d backend, symmetric tensors,
+DistributedDataParallel communication hooks and the CPU/gloo table executor.
+
+Importing this package registers the backend:
+
+    import stragglar_b200.parallel as sp
+    dist.init_process_group("stragglar")            # or "cpu:gloo,cuda:stragglar"
+    dist.all_reduce(x)                              # StragglAR AllReduce, straggler = last rank
+    sp.set_straggler(2)                             # physical rank 2 is the late one from now on
+    buf = sp.empty_symmetric(n, dtype=torch.float32, device="cuda")   # reduced in place, no staging
+
+Options can be given per process group (``sp.configure(alg="ring", blocks=32)``
+before ``init_process_group``) or through ``STRAGGLAR_*`` environment
+variables (ALG, STRAGGLER, PATH, BLOCKS, THREADS, TILE_BYTES, TIMEOUT_MS,
+ARENA_MB, STAGING_MB, CPU_ARENA_MB).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+_options: dict = {}
+_registered = False
+
+
+def _ext():
+    from . import _build_ext
+    return _build_ext.load()
+
+
+def configure(**options) -> None:
+    """Options of process groups created afterwards: alg, straggler, path
+    ('tma' | 'simt'), blocks, threads, tile_bytes, timeout_s, arena_bytes,
+    staging_bytes, schedule_text."""
+    _options.update(options)
+
+
+def _create(store, rank, size, timeout):
+    return _ext().create_backend(store, rank, size, timeout, dict(_options))
+
+
+def register() -> None:
+    """Register the backend name ``stragglar`` with torch.distributed
+    (cf. the reference's self-registering "dummy" backend,
+    implementation/custom_backend/include/dummy.hpp:106-111)."""
+    global _registered
+    if _registered:
+        return
+    import torch.distributed as dist
+    dist.Backend.register_backend("stragglar", _create, devices=["cpu", "cuda"])
+    _registered = True
+
+
+def backend_of(device="cuda", group=None):
+    """The stragglar Backend object serving ``device`` in ``group``."""
+    import torch
+    import torch.distributed as dist
+    pg = group if group is not None else dist.distributed_c10d._get_default_group()
+    return pg._get_backend(torch.device(device))
+
+
+def set_straggler(rank: int, device="cuda", group=None) -> None:
+    """Name the physical rank that is persistently late.  The schedule is
+    re-labelled so that this rank plays logical rank n-1; no device remapping
+    is needed (the reference swaps CUDA devices instead:
+    implementation/custom_backend/dp.py:71-77).  Call it on every rank."""
+    _ext().set_straggler(backend_of(device, group), rank)
+
+
+def set_algorithm(alg: str, device="cuda", group=None) -> None:
+    _ext().set_algorithm(backend_of(device, group), alg)
+
+
+def get_straggler(device="cuda", group=None) -> int:
+    return _ext().get_straggler(backend_of(device, group))
+
+
+def empty_symmetric(numel: int, dtype=None, device="cuda", group=None):
+    """A 1-D tensor in the backend's symmetric heap.  Collective: every rank
+    must call it with the same sizes in the same order."""
+    import torch
+    dev = torch.device(device)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    dtype = dtype or torch.float32
+    return _ext().alloc_symmetric(backend_of(dev, group), int(numel), dtype, dev.type == "cuda",
+                                  dev.index if dev.type == "cuda" else -1)
+
+
+def all_reduce_ex(tensor, average: bool = False, comm_dtype=None, group=None):
+    """AllReduce with the cast to ``comm_dtype`` fused into staging; returns a Work."""
+    return _ext().allreduce_ex(backend_of(tensor.device, group), tensor, average, comm_dtype)
+
+
+def check_status(device="cuda", group=None) -> int:
+    """Wait for the communication stream and return the device status word
+    (0 = ok; see ``stragglar_b200.compiler.status_string``)."""
+    import torch
+    return _ext().check_status(backend_of(device, group), torch.device(device).type == "cuda")
+
+
+def launches(device="cuda", group=None) -> int:
+    """Number of this library's kernels the backend has launched so far."""
+    return _ext().launches(backend_of(device, group))
+
+
+# ------------------------------------------------------------------ DDP hooks
+def fused_avg_hook(state, bucket):
+    """DDP communication hook: AllReduce the gradient bucket with the division
+    by world_size fused into the collective kernel (DDP's default path divides
+    in a separate pass before the AllReduce; the reference divides the flat
+    gradient after it, implementation/custom_backend/dp.py:59-60)."""
+    import torch.distributed as dist
+    group = state if state is not None else dist.group.WORLD
+    buf = bucket.buffer()
+    fut = dist.all_reduce(buf, op=dist.ReduceOp.AVG, group=group, async_op=True).get_future()
+    return fut.then(lambda f: f.value()[0])
+
+
+def bf16_fused_avg_hook(state, bucket):
+    """DDP communication hook: gradients travel as bfloat16.  The cast (and the
+    division by world_size) happen inside the staging pass and the kernel, not
+    as separate elementwise launches."""
+    import torch
+    buf = bucket.buffer()
+    work = all_reduce_ex(buf, average=True, comm_dtype=torch.bfloat16, group=state)
+    return work.get_future().then(lambda f: f.value()[0])
+
+
+register()

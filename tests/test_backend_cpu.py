@@ -1,0 +1,190 @@
+"""The c10d backend on CPU tensors: ranks are processes, arenas are POSIX
+shared memory, collectives walk the same tables as on the GPU.  Covers the
+Store bootstrap, Work/Future plumbing, every collective DDP needs, the
+straggler swap and DistributedDataParallel itself."""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn, args, errq):
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+        os.environ.setdefault("STRAGGLAR_TIMEOUT_MS", "20000")
+        import stragglar_b200.parallel  # noqa: F401
+        dist.init_process_group("stragglar", rank=rank, world_size=world)
+        fn(rank, world, *args)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
+def run_ranks(world, fn, *args):
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    msgs = []
+    while not errq.empty():
+        msgs.append(errq.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            msgs.append("a rank did not finish")
+    assert not msgs and all(p.exitcode == 0 for p in procs), "\n".join(msgs)
+
+
+def _seeded(rank, n, dtype=torch.float32):
+    g = torch.Generator().manual_seed(rank)
+    return torch.empty(n).uniform_(-1, 1, generator=g).to(dtype)
+
+
+def _collectives(rank, world):
+    import stragglar_b200.parallel as sp
+    n = 10_007
+    x = _seeded(rank, n)
+    want = torch.stack([_seeded(r, n).double() for r in range(world)]).sum(0)
+    y = x.clone()
+    work = dist.all_reduce(y, async_op=True)
+    work.wait()
+    assert work.is_completed() and work.get_future().done()
+    torch.testing.assert_close(y.double(), want, atol=1e-5, rtol=1e-6)
+    y = x.clone()
+    dist.all_reduce(y, op=dist.ReduceOp.AVG)
+    torch.testing.assert_close(y.double(), want / world, atol=1e-5, rtol=1e-6)
+    # the other algorithms through the same backend
+    for alg in ("ring", "stragglar_a2a", "direct", "rsag"):
+        sp.set_algorithm(alg, device="cpu")
+        y = x.clone()
+        dist.all_reduce(y)
+        torch.testing.assert_close(y.double(), want, atol=1e-5, rtol=1e-6)
+    sp.set_algorithm("stragglar", device="cpu")
+    # straggler swap: physical rank 1 plays the last logical rank
+    sp.set_straggler(1, device="cpu")
+    assert sp.get_straggler(device="cpu") == 1
+    y = x.clone()
+    dist.all_reduce(y)
+    torch.testing.assert_close(y.double(), want, atol=1e-5, rtol=1e-6)
+    # broadcast / all_gather / reduce_scatter / reduce / gather / scatter / all_to_all
+    b = torch.full((33,), float(rank))
+    dist.broadcast(b, src=world - 1)
+    assert (b == world - 1).all()
+    outs = [torch.empty(5) for _ in range(world)]
+    dist.all_gather(outs, torch.full((5,), float(rank)))
+    assert all((outs[r] == r).all() for r in range(world))
+    big = torch.empty(world * 7)
+    dist.all_gather_into_tensor(big, torch.full((7,), float(rank)))
+    assert torch.equal(big, torch.arange(world).repeat_interleave(7).float())
+    rs = torch.empty(11)
+    dist.reduce_scatter_tensor(rs, torch.arange(world * 11).float() + rank)
+    torch.testing.assert_close(rs, world * (torch.arange(11).float() + 11 * rank) + sum(range(world)))
+    r0 = x.clone()
+    dist.reduce(r0, dst=0)
+    if rank == 0:
+        torch.testing.assert_close(r0.double(), want, atol=1e-5, rtol=1e-6)
+    glist = [torch.empty(3) for _ in range(world)] if rank == 0 else None
+    dist.gather(torch.full((3,), float(rank)), glist, dst=0)
+    if rank == 0:
+        assert all((glist[r] == r).all() for r in range(world))
+    sc = torch.empty(4)
+    dist.scatter(sc, [torch.full((4,), float(10 + r)) for r in range(world)] if rank == 1 else None, src=1)
+    assert (sc == 10 + rank).all()
+    a2a = torch.empty(world * 2)
+    dist.all_to_all_single(a2a, torch.arange(world * 2).float() + 100 * rank)
+    want_a2a = torch.cat([torch.arange(2).float() + 2 * rank + 100 * p for p in range(world)])
+    assert torch.equal(a2a, want_a2a)
+    # point to point
+    if rank == 0:
+        dist.send(torch.arange(9).float(), dst=world - 1)
+    if rank == world - 1:
+        got = torch.empty(9)
+        dist.recv(got, src=0)
+        assert torch.equal(got, torch.arange(9).float())
+    # symmetric tensors are reduced in place without staging
+    s = sp.empty_symmetric(n, device="cpu")
+    s.copy_(x)
+    dist.all_reduce(s)
+    torch.testing.assert_close(s.double(), want, atol=1e-5, rtol=1e-6)
+    # half precisions
+    for dt, tol in ((torch.bfloat16, 6e-2), (torch.float16, 8e-3)):
+        h = _seeded(rank, 2050, dt)
+        wanth = torch.stack([_seeded(r, 2050, dt).double() for r in range(world)]).sum(0)
+        dist.all_reduce(h)
+        torch.testing.assert_close(h.double(), wanth, atol=tol, rtol=2e-2)
+    with pytest.raises(RuntimeError):
+        dist.all_reduce(torch.ones(4), op=dist.ReduceOp.MAX)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_collectives(world):
+    run_ranks(world, _collectives)
+
+
+def _ddp(rank, world):
+    import stragglar_b200.parallel as sp
+    from torch.nn.parallel import DistributedDataParallel as DDP
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    ref.load_state_dict(model.state_dict())
+    ddp = DDP(model, bucket_cap_mb=0.001)
+    ddp.register_comm_hook(None, sp.fused_avg_hook)
+    xs = [torch.randn(8, 16, generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+    ys = [torch.randn(8, 4, generator=torch.Generator().manual_seed(200 + r)) for r in range(world)]
+    loss = torch.nn.functional.mse_loss(ddp(xs[rank]), ys[rank])
+    loss.backward()
+    # reference: average of the per-rank gradients computed locally
+    total = None
+    for r in range(world):
+        ref.zero_grad()
+        torch.nn.functional.mse_loss(ref(xs[r]), ys[r]).backward()
+        g = [p.grad.clone() for p in ref.parameters()]
+        total = g if total is None else [a + b for a, b in zip(total, g)]
+    for p, g in zip(model.parameters(), total):
+        torch.testing.assert_close(p.grad, g / world, atol=1e-6, rtol=1e-5)
+
+
+def test_distributed_data_parallel_on_the_backend():
+    run_ranks(2, _ddp)
+
+
+def _late_rank_times_out(rank, world):
+    # rank 1 never joins this collective: rank 0's wait runs out and raises instead of hanging
+    import time
+    if rank == 0:
+        t0 = time.time()
+        with pytest.raises(RuntimeError, match="collective failed|timed out"):
+            dist.all_reduce(torch.ones(64))
+        assert time.time() - t0 < 5.0
+    else:
+        time.sleep(0.35)  # joins the final barrier while rank 0 is still giving up on the all-reduce
+    # afterwards both ranks meet again in the worker's final barrier (its own control channel)
+
+
+def test_missing_rank_raises_after_the_timeout():
+    os.environ["STRAGGLAR_TIMEOUT_MS"] = "700"
+    try:
+        run_ranks(2, _late_rank_times_out)
+    finally:
+        del os.environ["STRAGGLAR_TIMEOUT_MS"]
