@@ -172,6 +172,7 @@ def test_distributed_data_parallel_on_the_backend():
 def _late_rank_times_out(rank, world):
     # rank 1 never joins this collective: rank 0's wait runs out and raises instead of hanging
     import time
+    dist.barrier()   # the arenas exist from here on
     if rank == 0:
         t0 = time.time()
         with pytest.raises(RuntimeError, match="collective failed|timed out"):
