@@ -172,54 +172,87 @@ struct Item {
   uint32_t nelem;       // elements in the tile
 };
 
+// Geometry of the table resolved once per launch into shared memory, so that
+// walking the items needs no 64-bit division.
+#define SAR_MAX_ROUNDS 64
+struct OpGeom {
+  uint64_t elem0;      // first element of the op's first tile
+  uint64_t elem_end;   // end of the op's chunk
+  uint32_t ntiles;     // tiles the op covers
+  uint32_t tile0;      // its first tile within the chunk
+};
+struct RoundGeom { uint32_t op_begin, m, max_tiles, pad; };
+struct TableGeom {
+  OpGeom op[SAR_MAX_OPS];
+  RoundGeom round[SAR_MAX_ROUNDS];
+  uint32_t num_rounds;
+};
+
+// All threads of the block; ends with a block barrier.
+__device__ void resolve_table(const SarLaunchParams& P, TableGeom& G) {
+  const uint32_t nrounds = P.num_rounds < SAR_MAX_ROUNDS ? P.num_rounds : SAR_MAX_ROUNDS;
+  const uint32_t nops = nrounds ? P.round_begin[nrounds] : 0;
+  for (uint32_t o = threadIdx.x; o < nops && o < SAR_MAX_OPS; o += blockDim.x) {
+    const SarOp op = P.ops[o];
+    uint32_t t0, t1;
+    sar_part_range(sar_chunk_tiles(P.geom, op.chunk), op.part, op.parts, &t0, &t1);
+    const uint64_t cb = sar_chunk_begin(P.geom, op.chunk);
+    G.op[o].elem0 = cb + (uint64_t)t0 * P.geom.tile_elems;
+    G.op[o].elem_end = cb + sar_chunk_len(P.geom, op.chunk);
+    G.op[o].ntiles = t1 - t0;
+    G.op[o].tile0 = t0;
+  }
+  __syncthreads();
+  for (uint32_t r = threadIdx.x; r < nrounds; r += blockDim.x) {
+    const uint32_t ob = P.round_begin[r], oe = P.round_begin[r + 1];
+    uint32_t mx = 0;
+    for (uint32_t o = ob; o < oe; ++o) mx = G.op[o].ntiles > mx ? G.op[o].ntiles : mx;
+    G.round[r].op_begin = ob; G.round[r].m = oe - ob; G.round[r].max_tiles = mx;
+  }
+  if (threadIdx.x == 0) G.num_rounds = nrounds;
+  __syncthreads();
+}
+
 // Iterates the items of block `block` of `nblocks` in table order.
 struct ItemWalker {
   const SarLaunchParams* P;
+  const TableGeom* G;
   uint32_t block, nblocks;
   uint32_t ri;            // current round index
-  uint32_t ob, m, max_tiles;
-  uint64_t items, k, item_base;
-  __device__ void init(const SarLaunchParams* p, uint32_t b, uint32_t nb) {
-    P = p; block = b; nblocks = nb; ri = 0; item_base = 0;
+  uint32_t ob, m, items, k, base_mod;
+  __device__ void init(const SarLaunchParams* p, const TableGeom* g, uint32_t b, uint32_t nb) {
+    P = p; G = g; block = b; nblocks = nb; ri = 0; base_mod = 0;
     load_round();
   }
   __device__ void load_round() {
-    while (ri < P->num_rounds) {
-      ob = P->round_begin[ri];
-      const uint32_t oe = P->round_begin[ri + 1];
-      m = oe - ob;
-      max_tiles = 0;
-      for (uint32_t o = ob; o < oe; ++o) {
-        const uint32_t t = sar_op_tiles(P->geom, P->ops[o]);
-        max_tiles = t > max_tiles ? t : max_tiles;
-      }
-      items = (uint64_t)max_tiles * m;
-      k = ((uint64_t)block + nblocks - (item_base % nblocks)) % nblocks;
+    while (ri < G->num_rounds) {
+      ob = G->round[ri].op_begin;
+      m = G->round[ri].m;
+      items = G->round[ri].max_tiles * m;
+      k = (block + nblocks - base_mod) % nblocks;
       if (k < items) return;
-      item_base += items;
+      base_mod = (base_mod + items) % nblocks;
       ++ri;
     }
   }
   // false when the table is exhausted
   __device__ bool next(Item* it) {
-    while (ri < P->num_rounds) {
+    while (ri < G->num_rounds) {
       while (k < items) {
-        const SarOp* op = P->ops + ob + (uint32_t)(k % m);
-        const uint32_t lt = (uint32_t)(k / m);
+        const uint32_t o = ob + k % m;
+        const uint32_t lt = k / m;
         k += nblocks;
-        uint32_t t0, t1;
-        sar_part_range(sar_chunk_tiles(P->geom, op->chunk), op->part, op->parts, &t0, &t1);
-        if (lt >= t1 - t0) continue;
-        const uint32_t tile = t0 + lt;
-        const uint64_t cb = sar_chunk_begin(P->geom, op->chunk), cl = sar_chunk_len(P->geom, op->chunk);
-        const uint64_t e0 = cb + (uint64_t)tile * P->geom.tile_elems;
+        const OpGeom& og = G->op[o];
+        if (lt >= og.ntiles) continue;
+        const SarOp* op = P->ops + o;
+        const uint64_t e0 = og.elem0 + (uint64_t)lt * P->geom.tile_elems;
         uint64_t e1 = e0 + P->geom.tile_elems;
-        if (e1 > cb + cl) e1 = cb + cl;
-        it->op = op; it->tile = tile; it->fidx = sar_flag_index(P->geom, op->chunk, tile);
+        if (e1 > og.elem_end) e1 = og.elem_end;
+        it->op = op; it->tile = og.tile0 + lt; it->fidx = sar_flag_index(P->geom, op->chunk, og.tile0 + lt);
         it->elem0 = e0; it->nelem = (uint32_t)(e1 - e0);
         return true;
       }
-      item_base += items;
+      base_mod = (base_mod + items) % nblocks;
       ++ri;
       load_round();
     }
@@ -248,9 +281,15 @@ __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const 
   return true;
 }
 
+// Announces a finished tile.  The caller has ordered the tile's stores before
+// this call at system scope (fence_sys after the block barrier); the flags are
+// plain system-scope stores after that fence (release pattern).
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void publish_item(const SarLaunchParams& P, const SarOp* op, uint32_t fidx) {
-  st_release_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
-  if (op->kind == SAR_REDUCE_PUSH) st_release_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
+  st_relaxed_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
+  if (op->kind == SAR_REDUCE_PUSH) st_relaxed_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
 }
 
 // Sub-vector tail (fewer than 16 bytes) of a tile, element by element.
@@ -424,12 +463,14 @@ __device__ void leave_collective(const SarLaunchParams& P, const WaitCtx& w, uin
 
 template <typename T>
 __device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t nblocks) {
+  __shared__ TableGeom G;
   __shared__ Item s_item;
   __shared__ int s_state;   // 1: item ready, 0: table exhausted, -1: a wait failed
   WaitCtx w = enter_collective(P, block);
+  resolve_table(P, G);
   ItemWalker walk;
   uint32_t arrived = 1u << P.rank;
-  if (threadIdx.x == 0) walk.init(&P, block, nblocks);
+  if (threadIdx.x == 0) walk.init(&P, &G, block, nblocks);
   while (true) {
     if (threadIdx.x == 0) {
       Item it;
@@ -456,8 +497,8 @@ namespace tma {
 constexpr int kStages = 6;
 constexpr int kStageBytes = 32768;
 constexpr int kConsumerWarps = 4;
-constexpr int kThreads = 32 * (1 + kConsumerWarps);
-constexpr int kPendingFlags = 8;
+constexpr int kThreads = 32 * (2 + kConsumerWarps);   // producer warp, consumer warps, signal warp
+constexpr int kPendRing = 32;
 
 struct StageDesc {
   const SarOp* op;      // nullptr: no more work
@@ -470,12 +511,20 @@ struct StageDesc {
   uint32_t tail_elems;  // sub-vector tail of the item (handled with plain loads), last piece only
   uint64_t tail_elem0;
 };
+struct PendEntry { const SarOp* op; uint32_t fidx; uint32_t seq; };
 
 struct Shared {
   alignas(128) unsigned char ring[kStages][kStageBytes];
   alignas(8) uint64_t full[kStages];
   alignas(8) uint64_t empty[kStages];
   StageDesc desc[kStages];
+  TableGeom geom;
+  // finished items on their way to the signal warp
+  PendEntry pend[kPendRing];
+  uint32_t pend_tail;   // written by the storing thread
+  uint32_t pend_head;   // written by the signal thread
+  uint32_t landed;      // store groups with seq < landed have completed
+  uint32_t consumers_done;
   int abort_seen;
   uint32_t issued;      // pieces the producer has issued (written when it stops)
 };
@@ -530,6 +579,16 @@ template <int N> __device__ __forceinline__ void bulk_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kConsumerWarps) : "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_cta(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ uint32_t pow2_ceil(uint32_t x) {
   uint32_t p = 1;
@@ -538,6 +597,14 @@ __device__ __forceinline__ uint32_t pow2_ceil(uint32_t x) {
 }
 }  // namespace tma
 
+// Roles of a block (192 threads):
+//   warp 0, one thread   producer: walks the items, waits for their operands
+//                        (flags in peer memory), streams the tiles into the ring;
+//   warps 1-4            consumers: add the sources of a stage in place; one of
+//                        their threads issues the bulk stores and recycles stages;
+//   warp 5, one thread   signal: announces finished items (fence + flag stores).
+// Announcing costs a system-scope fence; doing it in a thread of its own keeps
+// the fence off the path that issues loads and stores.
 template <typename T>
 __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t nblocks, tma::Shared& S) {
   using namespace tma;
@@ -547,18 +614,18 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
   WaitCtx w = enter_collective(P, block);
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
-    S.abort_seen = 0;
-    S.issued = 0;
+    S.abort_seen = 0; S.issued = 0;
+    S.pend_tail = 0; S.pend_head = 0; S.landed = 0; S.consumers_done = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  __syncthreads();
+  resolve_table(P, S.geom);   // ends with a block barrier
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       ItemWalker walk;
-      walk.init(&P, block, nblocks);
+      walk.init(&P, &S.geom, block, nblocks);
       uint32_t arrived = 1u << P.rank;
       uint32_t seq = 0;           // pieces issued
       bool ok = true;
@@ -570,7 +637,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       };
       while (ok && walk.next(&it)) {
         if (!wait_item_ready(P, it, w, &arrived)) { ok = false; break; }
-        fence_proxy_async();   // flags were acquired through the generic proxy; the copies below use the async one
+        fence_proxy_async_global();   // flags were acquired through the generic proxy; the copies use the async one
         const SarOp* op = it.op;
         const bool local = op_reads_local(op);
         const uint32_t nsrc_total = op->nsrc + (local ? 1u : 0u);
@@ -614,34 +681,23 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       }
       S.issued = seq;
     }
-  } else {
+  } else if (warp <= (uint32_t)kConsumerWarps) {
     // --------------------------------------------------------------- consumers
     const uint32_t ctid = tid - 32;                 // 0 .. 127
     constexpr uint32_t CT = 32 * kConsumerWarps;
     uint32_t seq = 0;
-    // flags are published two store groups late, so that their data has landed
-    uint32_t pend_fidx[kPendingFlags];
-    const SarOp* pend_op[kPendingFlags];
-    uint32_t pend_seq[kPendingFlags] = {};
-    uint32_t pend_head = 0, pend_tail = 0;
-    auto flush_flags = [&](uint32_t complete_upto) {   // store groups with seq < complete_upto have landed
-      bool any = false;
-      while (pend_head != pend_tail && pend_seq[pend_head % kPendingFlags] < complete_upto) {
-        if (!any) { fence_proxy_async(); fence_sys(); any = true; }
-        publish_item(P, pend_op[pend_head % kPendingFlags], pend_fidx[pend_head % kPendingFlags]);
-        ++pend_head;
-      }
-    };
+    uint32_t landed = 0, pend_tail = 0;             // private copies of the storing thread (ctid 0)
     while (true) {
       const uint32_t s = seq % kStages;
       bool ok = true;
       if (lane == 0) {
-        if (ctid == 0 && pend_head != pend_tail && !mbar_try_wait(&S.full[s], (seq / kStages) & 1)) {
-          // The pipeline has run dry, perhaps because the producer waits for a
-          // tile that (through other ranks) depends on an item still held back
-          // here: announce everything now.
+        if (ctid == 0 && landed < seq && !mbar_try_wait(&S.full[s], (seq / kStages) & 1)) {
+          // The pipeline has run dry, perhaps because the producer waits for a tile
+          // that (through other ranks) depends on an item whose stores have not been
+          // reported as landed yet: report everything now.
           bulk_wait_all<0>();
-          flush_flags(0xffffffffu);
+          landed = seq;
+          st_release_cta(&S.landed, landed);
         }
         ok = mbar_wait(&S.full[s], (seq / kStages) & 1, w);
         if (*(volatile int*)&S.abort_seen) ok = false;
@@ -655,10 +711,32 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       if (op->kind != SAR_COPY && d.bytes) {
         const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
         const uint32_t nvec = d.bytes / 16;
-        for (uint32_t v = ctid; v < nvec; v += CT) {
+        const uint32_t nsrc = d.nsrc_total;
+        uint32_t v = ctid;
+        for (; v + 3 * CT < nvec; v += 4 * CT) {     // four independent vectors per thread
+          float acc[4][N];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) Vec<T>::unpack(*reinterpret_cast<const uint4*>(stage + (size_t)(v + u * CT) * 16), acc[u]);
+          for (uint32_t q = 1; q < nsrc; ++q) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              float f[N];
+              Vec<T>::unpack(*reinterpret_cast<const uint4*>(stage + (size_t)q * d.slot_bytes + (size_t)(v + u * CT) * 16), f);
+#pragma unroll
+              for (int i = 0; i < N; ++i) acc[u][i] += f[i];
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[u][i] *= scale;
+            *reinterpret_cast<uint4*>(stage + (size_t)(v + u * CT) * 16) = Vec<T>::pack(acc[u]);
+          }
+        }
+        for (; v < nvec; v += CT) {
           float acc[N];
           Vec<T>::unpack(*reinterpret_cast<const uint4*>(stage + (size_t)v * 16), acc);
-          for (uint32_t q = 1; q < d.nsrc_total; ++q) {
+          for (uint32_t q = 1; q < nsrc; ++q) {
             float f[N];
             Vec<T>::unpack(*reinterpret_cast<const uint4*>(stage + (size_t)q * d.slot_bytes + (size_t)v * 16), f);
 #pragma unroll
@@ -668,42 +746,71 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
           for (int i = 0; i < N; ++i) acc[i] *= scale;
           *reinterpret_cast<uint4*>(stage + (size_t)v * 16) = Vec<T>::pack(acc);
         }
-        fence_proxy_async();   // make the sums visible to the bulk store engine
+        fence_proxy_async_smem();   // make the sums visible to the bulk store engine
       }
       // Every consumer warp is done with this piece's descriptor and data, and
       // (a fortiori) with the previous piece's stage, which is released below.
       consumer_bar();
       if (ctid == 0) {
         if (d.bytes) {
-          fence_proxy_async();
           bulk_store((char*)P.comm.buf[P.rank] + d.byte_off, stage, d.bytes);
           if (op->kind == SAR_REDUCE_PUSH) bulk_store((char*)P.comm.buf[op->src[0]] + d.byte_off, stage, d.bytes);
         }
         bulk_commit();          // one group per piece (possibly empty), so group numbers follow seq
         if (d.last) {
-          if (d.tail_elems) scalar_elems<T>(P, op, d.tail_elem0, d.tail_elems);
-          pend_op[pend_tail % kPendingFlags] = op;
-          pend_fidx[pend_tail % kPendingFlags] = d.fidx;
-          pend_seq[pend_tail % kPendingFlags] = seq;
+          if (d.tail_elems) { scalar_elems<T>(P, op, d.tail_elem0, d.tail_elems); __threadfence_system(); }
+          // hand the item to the signal thread; wait (bounded) if its ring is full
+          if (pend_tail - ld_acquire_cta(&S.pend_head) >= (uint32_t)kPendRing) {
+            bulk_wait_all<0>();
+            landed = seq + 1;
+            st_release_cta(&S.landed, landed);
+            while (pend_tail - ld_acquire_cta(&S.pend_head) >= (uint32_t)kPendRing) {
+              if (*(volatile uint32_t*)w.abort_flag || globaltimer() > w.deadline) break;
+            }
+          }
+          PendEntry& e = S.pend[pend_tail % kPendRing];
+          e.op = op; e.fidx = d.fidx; e.seq = seq;
           ++pend_tail;
+          st_release_cta(&S.pend_tail, pend_tail);
         }
         // the previous piece's stores have read their stage: hand it back
         bulk_wait_read<1>();
         if (seq >= 1) mbar_arrive(&S.empty[(seq - 1) % kStages]);
-        // An item is announced once its last store group has landed.  Waiting for
-        // that right away would stall this thread for a store round trip per item,
-        // so the wait is taken two pieces late, and only if an item is due.
-        if (pend_head != pend_tail && pend_seq[pend_head % kPendingFlags] + 2 <= seq) {
-          bulk_wait_all<2>();          // groups up to seq-2 are complete
-          flush_flags(seq - 1);
-        }
-        if (pend_tail - pend_head >= (uint32_t)kPendingFlags - 1) { bulk_wait_all<0>(); flush_flags(seq + 1); }
+        // at most three store groups stay in flight; older ones have landed
+        bulk_wait_all<3>();
+        if (seq >= 3 && landed < seq - 2) { landed = seq - 2; st_release_cta(&S.landed, landed); }
       }
       ++seq;
     }
     if (ctid == 0) {
       bulk_wait_all<0>();
-      flush_flags(0xffffffffu);
+      st_release_cta(&S.landed, 0xffffffffu);
+      st_release_cta(&S.consumers_done, 1u);
+    }
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ signal
+    uint32_t head = 0;
+    while (true) {
+      const uint32_t done = ld_acquire_cta(&S.consumers_done);
+      const uint32_t tail = ld_acquire_cta(&S.pend_tail);
+      const uint32_t landed = ld_acquire_cta(&S.landed);
+      uint32_t n = 0;
+      while (head + n != tail && S.pend[(head + n) % kPendRing].seq < landed) ++n;
+      if (n) {
+        fence_proxy_async_global();   // the tiles were written by bulk copies
+        fence_sys();
+        for (uint32_t i = 0; i < n; ++i) {
+          const PendEntry& e = S.pend[(head + i) % kPendRing];
+          publish_item(P, e.op, e.fidx);
+        }
+        head += n;
+        st_release_cta(&S.pend_head, head);
+        continue;
+      }
+      if (done && head == tail) break;
+      if (*(volatile uint32_t*)w.abort_flag && done) break;
+      if (globaltimer() > w.deadline + 1000000000ull) break;   // the other roles have given up long ago
+      __nanosleep(64);
     }
   }
   __syncthreads();

@@ -1,0 +1,126 @@
+"""Run a compiled collective over plain ``torch.distributed`` send/recv (gloo).
+
+Every rank is a process with its own buffer; nothing is shared.  The op tables
+are pull based (the executing rank reads its peers), so each round is lowered
+to messages: the peers an op reads send their part of the chunk, the executor
+adds and stores, and a straggler matching sends the sum back.  Rounds are
+executed one after the other, as in the reference's hand-written
+ncclSend/ncclRecv schedules (stragglar/allreduce_4GPU.cu:299-368), which makes
+this executor the message-passing oracle for the schedule compiler and the
+CPU configuration of the benchmarks (4 ranks, 1 Mi fp32 elements, one rank
+5 ms late, checked against an fp64 sum).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..compiler import COPY, F_LOCAL, F_SCALE, REDUCE, REDUCE_PUSH, Program, Table
+
+
+def _chunk_bounds(count: int, esize: int, num_chunks: int) -> List[Tuple[int, int]]:
+    vw = max(1, 16 // esize)
+    nvec = count // vw
+    q, rem = divmod(nvec, num_chunks)
+    out = []
+    for c in range(num_chunks):
+        b = (q * c + min(c, rem)) * vw
+        e = (q * (c + 1) + min(c + 1, rem)) * vw if c < num_chunks - 1 else count
+        out.append((b, e))
+    return out
+
+
+def _op_range(bounds, op, tile_elems: int) -> Tuple[int, int]:
+    """Element range an op covers: part ``part`` of ``parts`` of the chunk's tiles."""
+    b, e = bounds[int(op["chunk"])]
+    tiles = -(-(e - b) // tile_elems)
+    part, parts = int(op["part"]), int(op["parts"])
+    t0, t1 = tiles * part // parts, tiles * (part + 1) // parts
+    return min(e, b + t0 * tile_elems), min(e, b + t1 * tile_elems)
+
+
+class GlooExecutor:
+    """Executes :class:`Program` objects on the default (or a given) process
+    group with point-to-point messages."""
+
+    def __init__(self, group=None, tile_elems: int = 4096):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.tile_elems = tile_elems
+        self.rounds_executed = 0
+
+    def _run_table(self, t: Table, buf: torch.Tensor, scale: float) -> None:
+        me = self.rank
+        if not t.takes_part(me):
+            return
+        bounds = _chunk_bounds(buf.numel(), buf.element_size(), t.num_chunks)
+        rounds = sorted({int(o["round"]) for r in t.ranks for o in r.ops})
+        for rnd in rounds:
+            # (executor, op index within the executor's round) identifies a message stream
+            first: List = []    # requests of the operand transfers
+            recv_bufs: Dict[Tuple[int, int, int], torch.Tensor] = {}
+            mine = []
+            for ex in range(self.world):
+                ops = [o for o in t.ranks[ex].ops if int(o["round"]) == rnd]
+                for k, op in enumerate(ops):
+                    lo, hi = _op_range(bounds, op, self.tile_elems)
+                    if hi <= lo:
+                        continue
+                    tag = (rnd * 64 + k) * 2
+                    for q in range(int(op["nsrc"])):
+                        src = int(op["src"][q])
+                        if ex == me:
+                            rb = torch.empty(hi - lo, dtype=buf.dtype)
+                            recv_bufs[(k, q, 0)] = rb
+                            first.append(dist.irecv(rb, src=src, group=self.group, tag=tag))
+                        elif src == me:
+                            first.append(dist.isend(buf[lo:hi].clone(), dst=ex, group=self.group, tag=tag))
+                    if ex == me:
+                        mine.append((k, op, lo, hi))
+            for r in first:
+                r.wait()
+            second: List = []
+            for k, op, lo, hi in mine:
+                kind, flags = int(op["kind"]), int(op["flags"])
+                if kind == COPY:
+                    buf[lo:hi] = recv_bufs[(k, 0, 0)]
+                    continue
+                acc = buf[lo:hi].float() if (kind == REDUCE_PUSH or flags & F_LOCAL) else torch.zeros(hi - lo)
+                for q in range(int(op["nsrc"])):
+                    acc = acc + recv_bufs[(k, q, 0)].float()
+                if flags & F_SCALE:
+                    acc = acc * scale
+                buf[lo:hi] = acc.to(buf.dtype)
+                if kind == REDUCE_PUSH:
+                    second.append(dist.isend(buf[lo:hi].clone(), dst=int(op["src"][0]), group=self.group,
+                                             tag=(rnd * 64 + k) * 2 + 1))
+            # the sums of straggler matchings executed by a peer come back into this rank's slot
+            for ex in range(self.world):
+                if ex == me:
+                    continue
+                ops = [o for o in t.ranks[ex].ops if int(o["round"]) == rnd]
+                for k, op in enumerate(ops):
+                    if int(op["kind"]) == REDUCE_PUSH and int(op["src"][0]) == me:
+                        lo, hi = _op_range(bounds, op, self.tile_elems)
+                        if hi > lo:
+                            second.append(dist.irecv(buf[lo:hi], src=ex, group=self.group, tag=(rnd * 64 + k) * 2 + 1))
+            for r in second:
+                r.wait()
+            self.rounds_executed += 1
+
+    def all_reduce(self, program: Program, buf: torch.Tensor, scale: float = 1.0, delay_s: float = 0.0) -> torch.Tensor:
+        """In-place collective on a contiguous 1-D CPU tensor.  ``delay_s`` makes
+        this rank late (an injected straggler delay on the host)."""
+        if program.n != self.world:
+            raise ValueError(f"program is for {program.n} ranks, group has {self.world}")
+        if not (buf.dim() == 1 and buf.is_contiguous() and buf.device.type == "cpu"):
+            raise ValueError("a contiguous 1-D CPU tensor is expected")
+        if delay_s > 0:
+            time.sleep(delay_s)
+        for t in program.phases:
+            self._run_table(t, buf, scale)
+        return buf
