@@ -17,7 +17,8 @@
 // start barrier (the reference times device 0 only); the delay is spun on
 // %globaltimer, so it lasts DELAY ms at any SM clock; extra columns follow the
 // reference's six.  Options come from STRAGGLAR_* environment variables (see
-// bench_common.h).
+// bench_common.h).  Each of <NUM_BYTES>, <ALG> and <DELAY> may be a
+// comma-separated list; the matrix then runs in one process.
 #include <algorithm>
 #include <cmath>
 
@@ -25,32 +26,30 @@
 
 using namespace bench;
 
-int main(int argc, char* argv[]) {
-  if (argc != 5) {
-    fprintf(stderr, "Usage: %s <bufferSize> <algorithm> <numIters> <sleepTimeMs>\n", argv[0]);
-    exit(EXIT_FAILURE);
+static std::vector<std::string> split_list(const char* s) {
+  std::vector<std::string> out;
+  std::string cur;
+  for (const char* p = s;; ++p) {
+    if (*p == ',' || *p == 0) { if (!cur.empty()) out.push_back(cur); cur.clear(); if (!*p) break; }
+    else cur.push_back(*p);
   }
-  const size_t bytes = (size_t)strtoull(argv[1], NULL, 10);
-  const char* alg = argv[2];
-  const int numIters = atoi(argv[3]);
-  const float sleepTime = (float)atof(argv[4]);
-  static const char* kAlgs[] = {"ring", "rhd", "direct", "stragglar", "stragglar_a2a", "rsag"};
-  if (std::none_of(std::begin(kAlgs), std::end(kAlgs), [&](const char* a) { return !strcmp(a, alg); })) {
-    fprintf(stderr, "Invalid algorithm: %s\n", alg);
-    exit(EXIT_FAILURE);
-  }
-  Options o = read_options();
+  return out;
+}
+
+// One (size, algorithm, delay) configuration on an existing communicator.
+static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const std::vector<int>& devs, size_t bytes,
+                      const char* alg, int numIters, float sleepTime, bool header) {
   const int n = o.ngpus;
   const uint32_t esize = dtype_size(o.dtype);
   const uint64_t count = bytes / esize;
   const int straggler = o.straggler >= 0 ? o.straggler : n - 1;
   const bool prephase = sleepTime >= 0;
-
   char err[512] = {0};
-  sar_program* prog = sar_program_build(alg, n, prephase ? 1 : 0, o.straggler, o.schedule_text.empty() ? nullptr : o.schedule_text.c_str(), err, sizeof err);
-  if (!prog) { fprintf(stderr, "%s\n", err); exit(EXIT_FAILURE); }
+  const char* sched = o.schedule_text.empty() ? nullptr : o.schedule_text.c_str();
+  sar_program* prog = sar_program_build(alg, n, prephase ? 1 : 0, o.straggler, sched, err, sizeof err);
+  if (!prog) { fprintf(stderr, "%s\n", err); return 1; }
   // roofline input: bytes the busiest rank moves in one direction after the straggler arrived
-  sar_program* post = sar_program_build(alg, n, sleepTime == 0 ? 1 : 0, o.straggler, o.schedule_text.empty() ? nullptr : o.schedule_text.c_str(), err, sizeof err);
+  sar_program* post = sar_program_build(alg, n, sleepTime == 0 ? 1 : 0, o.straggler, sched, err, sizeof err);
   double link_bytes = 0;
   for (int ph = 0; post && ph < sar_program_num_phases(post); ++ph) {
     const sar_table* t = sar_program_phase(post, ph);
@@ -59,13 +58,6 @@ int main(int argc, char* argv[]) {
     link_bytes += mx * (double)bytes / sar_table_num_chunks(t);
   }
   const double link_gbs = atof(env_str("STRAGGLAR_LINK_GBS", "770"));
-
-  std::vector<int> devs(n);
-  for (int i = 0; i < n; ++i) devs[i] = o.emulate ? 0 : i;
-  sar_local_comm* comm = sar_local_create(n, devs.data(), o.emulate ? 1 : 0, err, sizeof err);
-  if (!comm) { fprintf(stderr, "%s\n", err); exit(EXIT_FAILURE); }
-  Buffers B;
-  B.alloc(n, devs, count * esize);
 
   // the delay as the device really serves it
   double real_delay_ms = 0;
@@ -85,7 +77,8 @@ int main(int argc, char* argv[]) {
       best = ms < best ? ms : best;
     }
     real_delay_ms = best;
-    printf("Sleep: requested %.3f ms, measured %.3f ms on device %d\n", sleepTime, real_delay_ms, devs[straggler]);
+    CHECK_CUDA(cudaEventDestroy(a)); CHECK_CUDA(cudaEventDestroy(b));
+    if (header) printf("Sleep: requested %.3f ms, measured %.3f ms on device %d\n", sleepTime, real_delay_ms, devs[straggler]);
   }
 
   std::vector<uint64_t> seeds(n), delay_ns(n, 0);
@@ -97,7 +90,8 @@ int main(int argc, char* argv[]) {
   const float rtol = o.dtype == SAR_F32 ? 1e-6f : o.dtype == SAR_BF16 ? 0.02f : 0.004f;
   const bool is_sar = !strncmp(alg, "stragglar", 9);
 
-  printf("algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s),n,dtype,path,time_us_max,algbw_GBps,busbw_GBps,roofline_frac,real_delay_ms\n");
+  if (header)
+    printf("algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s),n,dtype,path,time_us_max,algbw_GBps,busbw_GBps,roofline_frac,real_delay_ms\n");
   int failures = 0;
   std::vector<float> ms(n);
   for (int iter = -o.warmup; iter < numIters; ++iter) {
@@ -142,7 +136,7 @@ int main(int argc, char* argv[]) {
         CHECK_CUDA(cudaSetDevice(devs[r]));
         uint32_t res[2] = {0, 0};
         if (o.const_fill) {
-          // all ones' sum: n(n+1)/2 -- checked through the same kernel with zero seeds would not apply; copy a sample
+          // constant inputs: every element must be n(n+1)/2 (the reference's check, on a 1 MiB sample)
           std::vector<char> h(std::min<size_t>(count * esize, 1 << 20));
           CHECK_CUDA(cudaMemcpy(h.data(), B.ptr[r], h.size(), cudaMemcpyDeviceToHost));
           const float want = n * (n + 1) / 2.0f;
@@ -158,7 +152,7 @@ int main(int argc, char* argv[]) {
         }
         if (res[0]) {
           float worst; memcpy(&worst, &res[1], 4);
-          fprintf(stderr, "VERIFY FAILED: iteration %d rank %d: %u wrong elements (max abs error %g)\n", iter, r, res[0], worst);
+          fprintf(stderr, "VERIFY FAILED: %s %zu B delay %.1f iteration %d rank %d: %u wrong elements (max abs error %g)\n", alg, bytes, sleepTime, iter, r, res[0], worst);
           ++failures;
         }
       }
@@ -175,10 +169,50 @@ int main(int argc, char* argv[]) {
     printf("%s,%zu,%d,%.3f,%.3f,%.3f,%d,%s,%s,%.1f,%.2f,%.2f,%.3f,%.3f\n", alg, (size_t)count * esize, iter + 1, sleepTime, t, bw, n,
            dtype_name(o.dtype), o.path == SAR_PATH_TMA ? "tma" : "simt", t * 1e3, algbw, busbw, net_ms > 0 ? roof_ms / net_ms : 0.0, real_delay_ms);
   }
-  B.release();
-  sar_local_destroy(comm);
   sar_program_free(prog);
   if (post) sar_program_free(post);
+  return failures;
+}
+
+int main(int argc, char* argv[]) {
+  if (argc != 5) {
+    fprintf(stderr, "Usage: %s <bufferSize> <algorithm> <numIters> <sleepTimeMs>\n", argv[0]);
+    exit(EXIT_FAILURE);
+  }
+  // every positional argument may be a comma-separated list: the whole matrix then runs in one
+  // process on one communicator (sizes outermost), which saves the start-up cost per configuration
+  const std::vector<std::string> sizes = split_list(argv[1]), algs = split_list(argv[2]), delays = split_list(argv[4]);
+  const int numIters = atoi(argv[3]);
+  static const char* kAlgs[] = {"ring", "rhd", "direct", "stragglar", "stragglar_a2a", "rsag"};
+  for (const auto& a : algs)
+    if (std::none_of(std::begin(kAlgs), std::end(kAlgs), [&](const char* k) { return a == k; })) {
+      fprintf(stderr, "Invalid algorithm: %s\n", a.c_str());
+      exit(EXIT_FAILURE);
+    }
+  if (sizes.empty() || algs.empty() || delays.empty()) { fprintf(stderr, "empty argument\n"); exit(EXIT_FAILURE); }
+  Options o = read_options();
+  const int n = o.ngpus;
+  size_t max_bytes = 0;
+  for (const auto& s : sizes) max_bytes = std::max(max_bytes, (size_t)strtoull(s.c_str(), NULL, 10));
+  char err[512] = {0};
+  std::vector<int> devs(n);
+  for (int i = 0; i < n; ++i) devs[i] = o.emulate ? 0 : i;
+  sar_local_comm* comm = sar_local_create(n, devs.data(), o.emulate ? 1 : 0, err, sizeof err);
+  if (!comm) { fprintf(stderr, "%s\n", err); exit(EXIT_FAILURE); }
+  Buffers B;
+  B.alloc(n, devs, max_bytes);
+  int failures = 0;
+  bool header = true;
+  for (const auto& s : sizes)
+    for (const auto& a : algs)
+      for (const auto& d : delays) {
+        if (a == "rhd" && (n & (n - 1))) { fprintf(stderr, "rhd needs a power-of-two GPU count; skipped\n"); continue; }
+        failures += run_config(comm, B, o, devs, (size_t)strtoull(s.c_str(), NULL, 10), a.c_str(), numIters, (float)atof(d.c_str()), header);
+        header = false;
+        fflush(stdout);
+      }
+  B.release();
+  sar_local_destroy(comm);
   for (int i = 0; i < n; ++i) printf("Rank %d, done\n", i);
   if (failures) { fprintf(stderr, "%d verification failures\n", failures); return 3; }
   return 0;
