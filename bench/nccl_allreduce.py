@@ -5,7 +5,7 @@ straggler (same %globaltimer kernel), the delay taken off for the bandwidth
 columns.
 
     torchrun --nproc-per-node=8 --master-addr 127.0.0.1 bench/nccl_allreduce.py \
-        --sizes 1048576,67108864,1073741824 --delays -1,5 --iters 20 --warmup 5
+        --sizes 1048576,67108864,1073741824 --delays=-1,5 --iters 20 --warmup 5
 
 Prints CSV rows with the columns of ``bin/allreduce`` (algorithm = nccl).
 A delay of -1 or 0 means no delay (NCCL has no pre-phase to hide).

@@ -23,7 +23,7 @@ struct Rank {
   uint64_t* trace = nullptr;   // 2 words
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool timed = false;
-  std::map<std::pair<const void*, int>, DevTable> tables;
+  std::map<std::pair<uint64_t, int>, DevTable> tables;   // keyed by the table's contents, not its address
 };
 }  // namespace
 
@@ -44,14 +44,27 @@ struct sar_local_comm {
     }                                                                                  \
   } while (0)
 
+static uint64_t fnv1a(uint64_t h, const void* p, size_t n) {
+  const unsigned char* c = (const unsigned char*)p;
+  for (size_t i = 0; i < n; ++i) { h ^= c[i]; h *= 0x100000001b3ull; }
+  return h;
+}
+
+// Device copy of a rank's table.  The cache is keyed by a hash of the table's
+// contents: programs come and go on the host, and a new one may live at the
+// address of one that was freed.
 static DevTable* upload(Rank& rk, const sar_table* t, int rank, char* err, int errlen) {
-  auto key = std::make_pair((const void*)t, rank);
+  const int nops = sar_table_num_ops(t, rank);
+  const int nrb = sar_table_num_round_begin(t, rank);
+  uint64_t h = 0xcbf29ce484222325ull;
+  if (nops) h = fnv1a(h, sar_table_ops(t, rank), sizeof(SarOp) * nops);
+  if (nrb) h = fnv1a(h, sar_table_round_begin(t, rank), sizeof(uint16_t) * nrb);
+  h = fnv1a(h, &nops, sizeof nops);
+  auto key = std::make_pair(h, rank);
   auto it = rk.tables.find(key);
   if (it != rk.tables.end()) return &it->second;
   DevTable* fail_value = nullptr;
   DevTable d;
-  const int nops = sar_table_num_ops(t, rank);
-  const int nrb = sar_table_num_round_begin(t, rank);
   CK(cudaMalloc(&d.ops, sizeof(SarOp) * (nops > 0 ? nops : 1)));
   CK(cudaMalloc(&d.round_begin, sizeof(uint16_t) * (nrb > 0 ? nrb : 1)));
   if (nops) CK(cudaMemcpy(d.ops, sar_table_ops(t, rank), sizeof(SarOp) * nops, cudaMemcpyHostToDevice));

@@ -1,4 +1,5 @@
-"""Run a compiled collective over plain ``torch.distributed`` send/recv (gloo).
+"""Run a compiled collective over plain ``torch.distributed`` send/recv
+(gloo for CPU tensors, NCCL for CUDA tensors).
 
 Every rank is a process with its own buffer; nothing is shared.  The op tables
 are pull based (the executing rank reads its peers), so each round is lowered
@@ -8,7 +9,10 @@ executed one after the other, as in the reference's hand-written
 ncclSend/ncclRecv schedules (stragglar/allreduce_4GPU.cu:299-368), which makes
 this executor the message-passing oracle for the schedule compiler and the
 CPU configuration of the benchmarks (4 ranks, 1 Mi fp32 elements, one rank
-5 ms late, checked against an fp64 sum).
+5 ms late, checked against an fp64 sum).  On CUDA tensors with the NCCL
+backend it is the baseline "what the reference's approach costs": the same
+tables executed as grouped ncclSend/ncclRecv plus separate add kernels, for
+any rank count (the reference has such code for 4 and 8 GPUs only).
 """
 from __future__ import annotations
 
@@ -42,7 +46,7 @@ def _op_range(bounds, op, tile_elems: int) -> Tuple[int, int]:
     return min(e, b + t0 * tile_elems), min(e, b + t1 * tile_elems)
 
 
-class GlooExecutor:
+class SendRecvExecutor:
     """Executes :class:`Program` objects on the default (or a given) process
     group with point-to-point messages."""
 
@@ -53,6 +57,12 @@ class GlooExecutor:
         self.tile_elems = tile_elems
         self.rounds_executed = 0
 
+    def _exchange(self, ops: List) -> None:
+        if not ops:
+            return
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+
     def _run_table(self, t: Table, buf: torch.Tensor, scale: float) -> None:
         me = self.rank
         if not t.takes_part(me):
@@ -60,67 +70,67 @@ class GlooExecutor:
         bounds = _chunk_bounds(buf.numel(), buf.element_size(), t.num_chunks)
         rounds = sorted({int(o["round"]) for r in t.ranks for o in r.ops})
         for rnd in rounds:
-            # (executor, op index within the executor's round) identifies a message stream
-            first: List = []    # requests of the operand transfers
-            recv_bufs: Dict[Tuple[int, int, int], torch.Tensor] = {}
+            # every rank walks (executor, op) in the same order, so the messages between a pair
+            # of ranks are issued in the same order on both sides (NCCL matches by order, not tag)
+            first: List = []
+            recv_bufs: Dict[Tuple[int, int], torch.Tensor] = {}
             mine = []
+            per_rank_ops = [[o for o in t.ranks[ex].ops if int(o["round"]) == rnd] for ex in range(self.world)]
             for ex in range(self.world):
-                ops = [o for o in t.ranks[ex].ops if int(o["round"]) == rnd]
-                for k, op in enumerate(ops):
+                for k, op in enumerate(per_rank_ops[ex]):
                     lo, hi = _op_range(bounds, op, self.tile_elems)
                     if hi <= lo:
                         continue
-                    tag = (rnd * 64 + k) * 2
                     for q in range(int(op["nsrc"])):
                         src = int(op["src"][q])
                         if ex == me:
-                            rb = torch.empty(hi - lo, dtype=buf.dtype)
-                            recv_bufs[(k, q, 0)] = rb
-                            first.append(dist.irecv(rb, src=src, group=self.group, tag=tag))
+                            rb = torch.empty(hi - lo, dtype=buf.dtype, device=buf.device)
+                            recv_bufs[(k, q)] = rb
+                            first.append(dist.P2POp(dist.irecv, rb, src, self.group))
                         elif src == me:
-                            first.append(dist.isend(buf[lo:hi].clone(), dst=ex, group=self.group, tag=tag))
+                            first.append(dist.P2POp(dist.isend, buf[lo:hi].clone(), ex, self.group))
                     if ex == me:
                         mine.append((k, op, lo, hi))
-            for r in first:
-                r.wait()
+            self._exchange(first)
             second: List = []
-            for k, op, lo, hi in mine:
-                kind, flags = int(op["kind"]), int(op["flags"])
-                if kind == COPY:
-                    buf[lo:hi] = recv_bufs[(k, 0, 0)]
-                    continue
-                acc = buf[lo:hi].float() if (kind == REDUCE_PUSH or flags & F_LOCAL) else torch.zeros(hi - lo)
-                for q in range(int(op["nsrc"])):
-                    acc = acc + recv_bufs[(k, q, 0)].float()
-                if flags & F_SCALE:
-                    acc = acc * scale
-                buf[lo:hi] = acc.to(buf.dtype)
-                if kind == REDUCE_PUSH:
-                    second.append(dist.isend(buf[lo:hi].clone(), dst=int(op["src"][0]), group=self.group,
-                                             tag=(rnd * 64 + k) * 2 + 1))
-            # the sums of straggler matchings executed by a peer come back into this rank's slot
             for ex in range(self.world):
-                if ex == me:
-                    continue
-                ops = [o for o in t.ranks[ex].ops if int(o["round"]) == rnd]
-                for k, op in enumerate(ops):
-                    if int(op["kind"]) == REDUCE_PUSH and int(op["src"][0]) == me:
-                        lo, hi = _op_range(bounds, op, self.tile_elems)
-                        if hi > lo:
-                            second.append(dist.irecv(buf[lo:hi], src=ex, group=self.group, tag=(rnd * 64 + k) * 2 + 1))
-            for r in second:
-                r.wait()
+                for k, op in enumerate(per_rank_ops[ex]):
+                    kind = int(op["kind"])
+                    lo, hi = _op_range(bounds, op, self.tile_elems)
+                    if hi <= lo:
+                        continue
+                    if ex == me:
+                        flags = int(op["flags"])
+                        if kind == COPY:
+                            buf[lo:hi] = recv_bufs[(k, 0)]
+                            continue
+                        acc = buf[lo:hi].float() if (kind == REDUCE_PUSH or flags & F_LOCAL) else torch.zeros(
+                            hi - lo, device=buf.device)
+                        for q in range(int(op["nsrc"])):
+                            acc = acc + recv_bufs[(k, q)].float()
+                        if flags & F_SCALE:
+                            acc = acc * scale
+                        buf[lo:hi] = acc.to(buf.dtype)
+                        if kind == REDUCE_PUSH:
+                            second.append(dist.P2POp(dist.isend, buf[lo:hi].clone(), int(op["src"][0]), self.group))
+                    elif kind == REDUCE_PUSH and int(op["src"][0]) == me:
+                        # the sum of a straggler matching executed by a peer comes back into this rank's slot
+                        second.append(dist.P2POp(dist.irecv, buf[lo:hi], ex, self.group))
+            self._exchange(second)
             self.rounds_executed += 1
 
     def all_reduce(self, program: Program, buf: torch.Tensor, scale: float = 1.0, delay_s: float = 0.0) -> torch.Tensor:
-        """In-place collective on a contiguous 1-D CPU tensor.  ``delay_s`` makes
+        """In-place collective on a contiguous 1-D tensor.  ``delay_s`` makes
         this rank late (an injected straggler delay on the host)."""
         if program.n != self.world:
             raise ValueError(f"program is for {program.n} ranks, group has {self.world}")
-        if not (buf.dim() == 1 and buf.is_contiguous() and buf.device.type == "cpu"):
-            raise ValueError("a contiguous 1-D CPU tensor is expected")
+        if not (buf.dim() == 1 and buf.is_contiguous()):
+            raise ValueError("a contiguous 1-D tensor is expected")
         if delay_s > 0:
             time.sleep(delay_s)
         for t in program.phases:
             self._run_table(t, buf, scale)
         return buf
+
+
+GlooExecutor = SendRecvExecutor
