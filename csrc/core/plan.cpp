@@ -323,7 +323,20 @@ Plan plan_rsag(int n) {
   return p;
 }
 
+bool default_push_copies() {
+  const char* v = getenv("STRAGGLAR_COPY");
+  if (v && *v) return std::string(v) != "pull";
+  return true;
+}
+
+static Plan plan_by_name_impl(const std::string& alg, int n, bool prephase, const Schedule* sched);
 Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* sched) {
+  Plan p = plan_by_name_impl(alg, n, prephase, sched);
+  p.push_copies = default_push_copies();
+  return p;
+}
+
+static Plan plan_by_name_impl(const std::string& alg, int n, bool prephase, const Schedule* sched) {
   if (alg == "stragglar") {
     Schedule s = sched ? *sched : builtin_schedule(n);
     if (s.n != n) throw CompileError("schedule is for n=" + std::to_string(s.n) + ", not " + std::to_string(n));
@@ -470,8 +483,21 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
       op.local_ver = (uint8_t)ver(s.dst);
       op.post_ver = (uint8_t)(ver(s.dst) + 1);
       if (s.kind == StepKind::Copy) {
-        op.kind = SAR_COPY;
-        ops[s.dst].push_back(op);
+        if (plan.push_copies) {
+          // executed by the source: it waits for its own slot (local_ver), for the destination
+          // slot's current version (src_ver) and stores into the destination
+          SarOp po = op;
+          po.kind = SAR_PUSH;
+          po.src[0] = (uint8_t)l2p[s.dst];
+          po.src_ver[0] = (uint8_t)ver(s.dst);
+          po.local_ver = (uint8_t)ver(s.srcs[0]);
+          po.post_ver = 0;
+          po.push_ver = (uint8_t)(ver(s.dst) + 1);
+          ops[s.srcs[0]].push_back(po);
+        } else {
+          op.kind = SAR_COPY;
+          ops[s.dst].push_back(op);
+        }
         out.chunks_in[l2p[s.dst]] += 1; out.chunks_out[l2p[s.srcs[0]]] += 1;
       } else if (s.kind == StepKind::Reduce) {
         op.kind = SAR_REDUCE;
@@ -561,6 +587,7 @@ Program build_program(const std::string& alg, int n, bool prephase, int straggle
   if (alg == "direct" && prephase && n > 2) {
     // phase 1: one-shot all-reduce among the n-1 non-stragglers, channel 1
     Plan sub = plan_rsag(n - 1);
+    sub.push_copies = default_push_copies();
     std::vector<int> submap(n - 1);
     for (int i = 0; i < n - 1; ++i) submap[i] = map.empty() ? i : map[i];
     Compiled c1 = compile(sub, submap, n);

@@ -64,6 +64,7 @@ struct Plan {
   std::vector<std::vector<uint32_t>> init;
   std::vector<int> participants;  // ranks whose result is checked
   Expect expect = Expect::AllReduce;
+  bool push_copies = false;       // lower Copy steps as SAR_PUSH (executed by the source) instead of SAR_COPY
   int num_rounds() const;
 };
 
@@ -81,6 +82,8 @@ Plan plan_direct(int n, bool prephase);
 Plan plan_reduce_scatter(int n);            // rank i ends with the sum of chunk i (n chunks)
 Plan plan_rsag(int n);                      // one-shot reduce-scatter + all-gather
 Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* sched = nullptr);
+// How Copy steps are lowered unless a plan says otherwise: STRAGGLAR_COPY=pull|push (default push).
+bool default_push_copies();
 
 struct RankTable {
   std::vector<SarOp> ops;

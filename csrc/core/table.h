@@ -11,6 +11,9 @@
 //   SAR_REDUCE       own[chunk] = (own[chunk] +) sum over nsrc peers
 //   SAR_REDUCE_PUSH  own[chunk] = peer[chunk] = own[chunk] + peer[chunk]
 //                    (the executing rank also stores the sum into the peer)
+//   SAR_PUSH         peer[chunk] = own[chunk]   (a copy executed by its source:
+//                    posted stores instead of loads over the link; the source
+//                    polls its own flags, the destination's flag is set remotely)
 //
 // Synchronisation is one 32-bit flag per (rank, chunk, tile), living in the
 // memory of the rank that owns the slot.  A flag holds `epoch_base + version`,
@@ -40,7 +43,7 @@
 #define SAR_FLAG_CAPACITY (1u << 18)     // flags per rank and channel
 #define SAR_VEC_BYTES 16
 
-enum SarOpKind : uint8_t { SAR_COPY = 0, SAR_REDUCE = 1, SAR_REDUCE_PUSH = 2 };
+enum SarOpKind : uint8_t { SAR_COPY = 0, SAR_REDUCE = 1, SAR_REDUCE_PUSH = 2, SAR_PUSH = 3 };
 enum SarOpFlag : uint8_t {
   SAR_F_SCALE = 1,  // multiply the result by the launch's scale (fused AVG / pre-division)
   SAR_F_LOCAL = 2,  // REDUCE: the own slot is one of the addends
@@ -65,13 +68,13 @@ struct SarOp {
   uint8_t chunk;
   uint8_t part;        // this op covers tile range `part` of `parts`
   uint8_t parts;
-  uint8_t nsrc;        // peers read (1 for COPY / REDUCE_PUSH)
+  uint8_t nsrc;        // peers read (1 for COPY / REDUCE_PUSH); PUSH: 1, src[0] is the destination
   uint8_t local_ver;   // version the own slot must have before it is read or overwritten
   uint8_t post_ver;    // version of the own slot after this op
-  uint8_t push_ver;    // REDUCE_PUSH: version of the peer slot after this op
+  uint8_t push_ver;    // REDUCE_PUSH / PUSH: version of the peer slot after this op
   uint8_t pad[2];
   uint8_t src[SAR_MAX_RANKS];      // peer ranks (physical)
-  uint8_t src_ver[SAR_MAX_RANKS];  // version needed of each peer's slot
+  uint8_t src_ver[SAR_MAX_RANKS];  // version needed of each peer's slot (PUSH: the version it replaces)
 };
 static_assert(sizeof(SarOp) == 12 + 2 * SAR_MAX_RANKS, "SarOp layout");
 

@@ -288,8 +288,9 @@ __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void publish_item(const SarLaunchParams& P, const SarOp* op, uint32_t fidx) {
-  st_relaxed_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
-  if (op->kind == SAR_REDUCE_PUSH) st_relaxed_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
+  if (op->kind != SAR_PUSH) st_relaxed_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
+  if (op->kind == SAR_REDUCE_PUSH || op->kind == SAR_PUSH)
+    st_relaxed_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
 }
 
 // Sub-vector tail (fewer than 16 bytes) of a tile, element by element.
@@ -301,6 +302,7 @@ __device__ void scalar_elems(const SarLaunchParams& P, const SarOp* op, uint64_t
   for (uint32_t i = 0; i < n; ++i) {
     const uint64_t off = (e0 + i) * sizeof(T);
     float acc;
+    if (op->kind == SAR_PUSH) { Vec<T>::store1((char*)P.comm.buf[op->src[0]] + off, Vec<T>::load1(own + off)); continue; }
     if (op->kind == SAR_COPY) acc = Vec<T>::load1((char*)P.comm.buf[op->src[0]] + off);
     else {
       acc = local ? Vec<T>::load1(own + off) : 0.0f;
@@ -321,17 +323,19 @@ __device__ void simt_tile(const SarLaunchParams& P, const Item& it) {
   const uint64_t byte0 = it.elem0 * sizeof(T);
   char* own = (char*)P.comm.buf[P.rank] + byte0;
   const uint32_t tid = threadIdx.x, nth = blockDim.x;
-  if (op->kind == SAR_COPY) {
-    const char* src = (const char*)P.comm.buf[op->src[0]] + byte0;
+  if (op->kind == SAR_COPY || op->kind == SAR_PUSH) {
+    const char* peer = (const char*)P.comm.buf[op->src[0]] + byte0;
+    const char* src = op->kind == SAR_COPY ? peer : own;
+    char* dst = op->kind == SAR_COPY ? own : const_cast<char*>(peer);
     uint32_t v = tid;
     for (; v + (UNROLL - 1) * nth < nvec; v += UNROLL * nth) {
       uint4 r[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) r[u] = ld_vec_sys(src + (size_t)(v + u * nth) * 16);
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) st_vec(own + (size_t)(v + u * nth) * 16, r[u]);
+      for (int u = 0; u < UNROLL; ++u) st_vec(dst + (size_t)(v + u * nth) * 16, r[u]);
     }
-    for (; v < nvec; v += nth) st_vec(own + (size_t)v * 16, ld_vec_sys(src + (size_t)v * 16));
+    for (; v < nvec; v += nth) st_vec(dst + (size_t)v * 16, ld_vec_sys(src + (size_t)v * 16));
   } else {
     const bool local = op_reads_local(op);
     const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
@@ -639,8 +643,10 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         if (!wait_item_ready(P, it, w, &arrived)) { ok = false; break; }
         fence_proxy_async_global();   // flags were acquired through the generic proxy; the copies use the async one
         const SarOp* op = it.op;
-        const bool local = op_reads_local(op);
-        const uint32_t nsrc_total = op->nsrc + (local ? 1u : 0u);
+        const bool push_only = op->kind == SAR_PUSH;            // the only source is the own slot
+        const bool local = push_only || op_reads_local(op);
+        const uint32_t npeer = push_only ? 0u : op->nsrc;
+        const uint32_t nsrc_total = npeer + (local ? 1u : 0u);
         const uint32_t slot_bytes = kStageBytes / pow2_ceil(nsrc_total);
         const uint32_t vec_bytes = (it.nelem / N) * 16u;
         const uint32_t tail = it.nelem % N;
@@ -657,10 +663,10 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
           d.tail_elem0 = it.elem0 + (uint64_t)(it.nelem / N) * N;
           if (bytes) {
             mbar_arrive_expect_tx(&S.full[s], bytes * nsrc_total);
-            for (uint32_t q = 0; q < op->nsrc; ++q)
+            for (uint32_t q = 0; q < npeer; ++q)
               bulk_load(&S.ring[s][q * slot_bytes], (const char*)P.comm.buf[op->src[q]] + d.byte_off, bytes, &S.full[s]);
             if (local)
-              bulk_load(&S.ring[s][op->nsrc * slot_bytes], (const char*)P.comm.buf[P.rank] + d.byte_off, bytes, &S.full[s]);
+              bulk_load(&S.ring[s][npeer * slot_bytes], (const char*)P.comm.buf[P.rank] + d.byte_off, bytes, &S.full[s]);
           } else {
             mbar_arrive(&S.full[s]);   // an item that is only a sub-vector tail
           }
@@ -708,7 +714,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       if (d.op == nullptr) break;
       const SarOp* op = d.op;
       unsigned char* stage = S.ring[s];
-      if (op->kind != SAR_COPY && d.bytes) {
+      if (op->kind != SAR_COPY && op->kind != SAR_PUSH && d.bytes) {
         const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
         const uint32_t nvec = d.bytes / 16;
         const uint32_t nsrc = d.nsrc_total;
@@ -753,8 +759,9 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       consumer_bar();
       if (ctid == 0) {
         if (d.bytes) {
-          bulk_store((char*)P.comm.buf[P.rank] + d.byte_off, stage, d.bytes);
-          if (op->kind == SAR_REDUCE_PUSH) bulk_store((char*)P.comm.buf[op->src[0]] + d.byte_off, stage, d.bytes);
+          if (op->kind != SAR_PUSH) bulk_store((char*)P.comm.buf[P.rank] + d.byte_off, stage, d.bytes);
+          if (op->kind == SAR_REDUCE_PUSH || op->kind == SAR_PUSH)
+            bulk_store((char*)P.comm.buf[op->src[0]] + d.byte_off, stage, d.bytes);
         }
         bulk_commit();          // one group per piece (possibly empty), so group numbers follow seq
         if (d.last) {

@@ -33,7 +33,7 @@ OP_DTYPE = np.dtype([
     ("nsrc", "u1"), ("local_ver", "u1"), ("post_ver", "u1"), ("push_ver", "u1"), ("pad", "u1", (2,)),
     ("src", "u1", (MAX_RANKS,)), ("src_ver", "u1", (MAX_RANKS,)),
 ])
-COPY, REDUCE, REDUCE_PUSH = 0, 1, 2
+COPY, REDUCE, REDUCE_PUSH, PUSH = 0, 1, 2, 3
 F_SCALE, F_LOCAL = 1, 2
 DTYPES = {"float32": 0, "bfloat16": 1, "float16": 2}
 ALGORITHMS = ("stragglar", "stragglar_a2a", "ring", "rhd", "direct", "rsag", "reducescatter")

@@ -22,7 +22,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from ..compiler import COPY, F_LOCAL, F_SCALE, REDUCE, REDUCE_PUSH, Program, Table
+from ..compiler import COPY, F_LOCAL, F_SCALE, PUSH, REDUCE, REDUCE_PUSH, Program, Table
 
 
 def _chunk_bounds(count: int, esize: int, num_chunks: int) -> List[Tuple[int, int]]:
@@ -75,11 +75,22 @@ class SendRecvExecutor:
             first: List = []
             recv_bufs: Dict[Tuple[int, int], torch.Tensor] = {}
             mine = []
+            landed: List = []
             per_rank_ops = [[o for o in t.ranks[ex].ops if int(o["round"]) == rnd] for ex in range(self.world)]
             for ex in range(self.world):
                 for k, op in enumerate(per_rank_ops[ex]):
                     lo, hi = _op_range(bounds, op, self.tile_elems)
                     if hi <= lo:
+                        continue
+                    if int(op["kind"]) == PUSH:
+                        # a copy executed by its source: one message from the executor to op.src[0]
+                        dst = int(op["src"][0])
+                        if ex == me:
+                            first.append(dist.P2POp(dist.isend, buf[lo:hi].clone(), dst, self.group))
+                        elif dst == me:
+                            rb = torch.empty(hi - lo, dtype=buf.dtype, device=buf.device)
+                            first.append(dist.P2POp(dist.irecv, rb, ex, self.group))
+                            landed.append((rb, lo, hi))
                         continue
                     for q in range(int(op["nsrc"])):
                         src = int(op["src"][q])
@@ -92,12 +103,16 @@ class SendRecvExecutor:
                     if ex == me:
                         mine.append((k, op, lo, hi))
             self._exchange(first)
+            for rb, lo, hi in landed:      # chunks that peers pushed into this rank's slots
+                buf[lo:hi] = rb
             second: List = []
             for ex in range(self.world):
                 for k, op in enumerate(per_rank_ops[ex]):
                     kind = int(op["kind"])
                     lo, hi = _op_range(bounds, op, self.tile_elems)
                     if hi <= lo:
+                        continue
+                    if kind == PUSH:
                         continue
                     if ex == me:
                         flags = int(op["flags"])
