@@ -156,7 +156,8 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
       if (op.kind == SAR_COPY) {
         memcpy((char*)v.buf[me] + e0 * g.esize, (const char*)v.buf[op.src[0]] + e0 * g.esize, (e1 - e0) * g.esize);
       } else if (op.kind == SAR_PUSH) {
-        memcpy((char*)v.buf[op.src[0]] + e0 * g.esize, (const char*)v.buf[me] + e0 * g.esize, (e1 - e0) * g.esize);
+        for (int q = 0; q < op.nsrc; ++q)
+          memcpy((char*)v.buf[op.src[q]] + e0 * g.esize, (const char*)v.buf[me] + e0 * g.esize, (e1 - e0) * g.esize);
       } else {
         for (uint64_t e = e0; e < e1; ++e) {
           float acc = reads_local ? load_elem(v.buf[me], e, l.dtype) : 0.0f;
@@ -167,8 +168,11 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
         }
       }
       if (op.kind != SAR_PUSH) v.flags[me][fidx].store(l.epoch_base + op.post_ver, std::memory_order_release);
-      if (op.kind == SAR_REDUCE_PUSH || op.kind == SAR_PUSH)
+      if (op.kind == SAR_REDUCE_PUSH)
         v.flags[op.src[0]][fidx].store(l.epoch_base + op.push_ver, std::memory_order_release);
+      if (op.kind == SAR_PUSH)
+        for (int q = 0; q < op.nsrc; ++q)
+          v.flags[op.src[q]][fidx].store(l.epoch_base + op.push_ver, std::memory_order_release);
     }
     item_base += items;
   }

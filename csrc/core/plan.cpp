@@ -564,6 +564,29 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
                            std::to_string(c));
     }
   }
+  // A rank that pushes the same tiles of one chunk to several peers in one round loads them
+  // once: merge those pushes into one op with several destinations.
+  for (int lr = 0; lr < n; ++lr) {
+    std::vector<SarOp> merged;
+    for (const SarOp& op : ops[lr]) {
+      bool done = false;
+      if (op.kind == SAR_PUSH) {
+        for (SarOp& m : merged) {
+          if (m.kind == SAR_PUSH && m.round == op.round && m.chunk == op.chunk && m.part == op.part &&
+              m.parts == op.parts && m.local_ver == op.local_ver && m.push_ver == op.push_ver &&
+              m.nsrc < SAR_MAX_RANKS - 1) {
+            m.src[m.nsrc] = op.src[0];
+            m.src_ver[m.nsrc] = op.src_ver[0];
+            ++m.nsrc;
+            done = true;
+            break;
+          }
+        }
+      }
+      if (!done) merged.push_back(op);
+    }
+    ops[lr] = merged;
+  }
   for (int pr = 0; pr < np; ++pr) out.ranks[pr].round_begin.assign(1, 0);
   for (int lr = 0; lr < n; ++lr) {
     RankTable& t = out.ranks[l2p[lr]];

@@ -11,9 +11,10 @@
 //   SAR_REDUCE       own[chunk] = (own[chunk] +) sum over nsrc peers
 //   SAR_REDUCE_PUSH  own[chunk] = peer[chunk] = own[chunk] + peer[chunk]
 //                    (the executing rank also stores the sum into the peer)
-//   SAR_PUSH         peer[chunk] = own[chunk]   (a copy executed by its source:
-//                    posted stores instead of loads over the link; the source
-//                    polls its own flags, the destination's flag is set remotely)
+//   SAR_PUSH         peer[chunk] = own[chunk] for nsrc peers (a copy executed by
+//                    its source: posted stores instead of loads over the link;
+//                    the source polls its own flags, loads a tile once and
+//                    stores it to every destination, whose flags it sets remotely)
 //
 // Synchronisation is one 32-bit flag per (rank, chunk, tile), living in the
 // memory of the rank that owns the slot.  A flag holds `epoch_base + version`,
@@ -68,7 +69,7 @@ struct SarOp {
   uint8_t chunk;
   uint8_t part;        // this op covers tile range `part` of `parts`
   uint8_t parts;
-  uint8_t nsrc;        // peers read (1 for COPY / REDUCE_PUSH); PUSH: 1, src[0] is the destination
+  uint8_t nsrc;        // peers read (1 for COPY / REDUCE_PUSH); PUSH: the destinations src[0..nsrc)
   uint8_t local_ver;   // version the own slot must have before it is read or overwritten
   uint8_t post_ver;    // version of the own slot after this op
   uint8_t push_ver;    // REDUCE_PUSH / PUSH: version of the peer slot after this op

@@ -199,6 +199,13 @@ template <typename K> int allow_smem(K kernel, size_t bytes) {
 extern "C" {
 
 int sar_cuda_default_blocks(int path) { return path == SAR_PATH_TMA ? 32 : 64; }
+int sar_cuda_pick_blocks(int path, uint64_t bytes) {
+  const uint64_t b = bytes / (2ull << 20);
+  const int lo = 16, hi = 128;
+  (void)path;
+  return (int)(b < (uint64_t)lo ? lo : (b > (uint64_t)hi ? hi : b));
+}
+uint32_t sar_cuda_default_tile_bytes(int path) { return path == SAR_PATH_TMA ? (64u << 10) : (128u << 10); }
 
 int sar_cuda_launch(const SarLaunchParams* p, int path, int blocks, int threads, void* stream) {
   if (blocks <= 0) blocks = sar_cuda_default_blocks(path);

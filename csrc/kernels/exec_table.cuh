@@ -289,8 +289,9 @@ __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
 }
 __device__ __forceinline__ void publish_item(const SarLaunchParams& P, const SarOp* op, uint32_t fidx) {
   if (op->kind != SAR_PUSH) st_relaxed_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
-  if (op->kind == SAR_REDUCE_PUSH || op->kind == SAR_PUSH)
-    st_relaxed_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
+  if (op->kind == SAR_REDUCE_PUSH) st_relaxed_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
+  if (op->kind == SAR_PUSH)
+    for (int q = 0; q < op->nsrc; ++q) st_relaxed_sys(P.comm.flags[op->src[q]] + fidx, P.epoch_base + op->push_ver);
 }
 
 // Sub-vector tail (fewer than 16 bytes) of a tile, element by element.
@@ -302,7 +303,11 @@ __device__ void scalar_elems(const SarLaunchParams& P, const SarOp* op, uint64_t
   for (uint32_t i = 0; i < n; ++i) {
     const uint64_t off = (e0 + i) * sizeof(T);
     float acc;
-    if (op->kind == SAR_PUSH) { Vec<T>::store1((char*)P.comm.buf[op->src[0]] + off, Vec<T>::load1(own + off)); continue; }
+    if (op->kind == SAR_PUSH) {
+      const float v = Vec<T>::load1(own + off);
+      for (int q = 0; q < op->nsrc; ++q) Vec<T>::store1((char*)P.comm.buf[op->src[q]] + off, v);
+      continue;
+    }
     if (op->kind == SAR_COPY) acc = Vec<T>::load1((char*)P.comm.buf[op->src[0]] + off);
     else {
       acc = local ? Vec<T>::load1(own + off) : 0.0f;
@@ -324,18 +329,24 @@ __device__ void simt_tile(const SarLaunchParams& P, const Item& it) {
   char* own = (char*)P.comm.buf[P.rank] + byte0;
   const uint32_t tid = threadIdx.x, nth = blockDim.x;
   if (op->kind == SAR_COPY || op->kind == SAR_PUSH) {
-    const char* peer = (const char*)P.comm.buf[op->src[0]] + byte0;
-    const char* src = op->kind == SAR_COPY ? peer : own;
-    char* dst = op->kind == SAR_COPY ? own : const_cast<char*>(peer);
+    const bool push = op->kind == SAR_PUSH;
+    const char* src = push ? own : (const char*)P.comm.buf[op->src[0]] + byte0;
+    const int ndst = push ? op->nsrc : 1;
     uint32_t v = tid;
     for (; v + (UNROLL - 1) * nth < nvec; v += UNROLL * nth) {
       uint4 r[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) r[u] = ld_vec_sys(src + (size_t)(v + u * nth) * 16);
+      for (int q = 0; q < ndst; ++q) {
+        char* dst = push ? (char*)P.comm.buf[op->src[q]] + byte0 : own;
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) st_vec(dst + (size_t)(v + u * nth) * 16, r[u]);
+        for (int u = 0; u < UNROLL; ++u) st_vec(dst + (size_t)(v + u * nth) * 16, r[u]);
+      }
     }
-    for (; v < nvec; v += nth) st_vec(dst + (size_t)v * 16, ld_vec_sys(src + (size_t)v * 16));
+    for (; v < nvec; v += nth) {
+      const uint4 r = ld_vec_sys(src + (size_t)v * 16);
+      for (int q = 0; q < ndst; ++q) st_vec((push ? (char*)P.comm.buf[op->src[q]] + byte0 : own) + (size_t)v * 16, r);
+    }
   } else {
     const bool local = op_reads_local(op);
     const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
@@ -760,8 +771,9 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       if (ctid == 0) {
         if (d.bytes) {
           if (op->kind != SAR_PUSH) bulk_store((char*)P.comm.buf[P.rank] + d.byte_off, stage, d.bytes);
-          if (op->kind == SAR_REDUCE_PUSH || op->kind == SAR_PUSH)
-            bulk_store((char*)P.comm.buf[op->src[0]] + d.byte_off, stage, d.bytes);
+          if (op->kind == SAR_REDUCE_PUSH) bulk_store((char*)P.comm.buf[op->src[0]] + d.byte_off, stage, d.bytes);
+          if (op->kind == SAR_PUSH)
+            for (int q = 0; q < op->nsrc; ++q) bulk_store((char*)P.comm.buf[op->src[q]] + d.byte_off, stage, d.bytes);
         }
         bulk_commit();          // one group per piece (possibly empty), so group numbers follow seq
         if (d.last) {

@@ -24,6 +24,10 @@ int sar_cuda_launch(const struct SarLaunchParams* p, int path, int blocks, int t
 int sar_cuda_launch_emulated(const struct SarLaunchParams* d_params, int n, int dtype, int path, int blocks_per_rank,
                              int threads, void* stream);
 int sar_cuda_default_blocks(int path);
+// blocks per rank for a buffer of `bytes`: few for small messages (latency bound, and the SMs
+// are left to the compute that overlaps the collective), up to 128 for large ones
+int sar_cuda_pick_blocks(int path, uint64_t bytes);
+uint32_t sar_cuda_default_tile_bytes(int path);
 int sar_cuda_max_emulated_blocks(int dtype, int path, int threads);   // resident blocks on the current device
 
 // Barrier across ranks on control channel `channel`: announces `epoch` and

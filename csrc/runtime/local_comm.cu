@@ -157,9 +157,10 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
     if (((uintptr_t)bufs[r]) & 15) { if (err) snprintf(err, errlen, "buffer of rank %d is not 16-byte aligned", r); return 1; }
   const uint32_t esize = dtype == SAR_F32 ? 4 : 2;
   const int path = o->path;
-  int blocks = o->blocks > 0 ? o->blocks : sar_cuda_default_blocks(path);
+  int blocks = o->blocks > 0 ? o->blocks : sar_cuda_pick_blocks(path, count * esize);
+  if (c->emulate && o->blocks <= 0) blocks = 4;   // all ranks share one device
   const double timeout_s = o->timeout_s > 0 ? o->timeout_s : 10.0;
-  const uint32_t tile_max = o->tile_bytes ? o->tile_bytes : (128u << 10);
+  const uint32_t tile_max = o->tile_bytes ? o->tile_bytes : sar_cuda_default_tile_bytes(path);
   std::vector<bool> delayed(n, false);
 
   if (o->timed) {

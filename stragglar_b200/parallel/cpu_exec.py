@@ -83,14 +83,15 @@ class SendRecvExecutor:
                     if hi <= lo:
                         continue
                     if int(op["kind"]) == PUSH:
-                        # a copy executed by its source: one message from the executor to op.src[0]
-                        dst = int(op["src"][0])
-                        if ex == me:
-                            first.append(dist.P2POp(dist.isend, buf[lo:hi].clone(), dst, self.group))
-                        elif dst == me:
-                            rb = torch.empty(hi - lo, dtype=buf.dtype, device=buf.device)
-                            first.append(dist.P2POp(dist.irecv, rb, ex, self.group))
-                            landed.append((rb, lo, hi))
+                        # a copy executed by its source: one message from the executor to every destination
+                        for q in range(int(op["nsrc"])):
+                            dst = int(op["src"][q])
+                            if ex == me:
+                                first.append(dist.P2POp(dist.isend, buf[lo:hi].clone(), dst, self.group))
+                            elif dst == me:
+                                rb = torch.empty(hi - lo, dtype=buf.dtype, device=buf.device)
+                                first.append(dist.P2POp(dist.irecv, rb, ex, self.group))
+                                landed.append((rb, lo, hi))
                         continue
                     for q in range(int(op["nsrc"])):
                         src = int(op["src"][q])
