@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <pybind11/chrono.h>
 #include <torch/extension.h>
 
@@ -24,6 +25,11 @@ namespace sarpg {
   } while (0)
 
 namespace {
+// NVTX range around the host side of every collective (visible in Nsight Systems)
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
 constexpr int kBarrierChannel = 2;   // control words of barrier() and the staged collectives
 constexpr int kP2PChannel = 3;       // flag words of send/recv handshakes
 
@@ -248,7 +254,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.geom = g; P.rank = me; P.nranks = n; P.participants = c.participants;
       P.epoch_base = epoch; P.scale = scale; P.dtype = dt;
       P.timeout_ns = (uint64_t)(opts_.timeout_s * 1e9);
-      P.status = t.status(); P.trace = nullptr; P.delay_ns = 0;
+      P.status = t.status(); P.trace = reinterpret_cast<uint64_t*>(t.status() + 4); P.delay_ns = 0;
       SAR_CUDA_CHECK(sar_cuda_launch(&P, opts_.path, blocks, opts_.threads, s.stream->stream()));
       ++launches_;
     } else {
@@ -287,6 +293,16 @@ int64_t ProcessGroupStragglar::check_status(bool cuda) {
     }
   }
   return st;
+}
+
+std::pair<int64_t, int64_t> ProcessGroupStragglar::last_trace() {
+  Side& s = cuda_;
+  if (!s.t) return {0, 0};
+  SAR_CUDA_CHECK(cudaSetDevice(s.device));
+  SAR_CUDA_CHECK(cudaStreamSynchronize(s.stream->stream()));
+  uint64_t v[2] = {0, 0};
+  SAR_CUDA_CHECK(cudaMemcpy(v, s.t->status() + 4, 16, cudaMemcpyDeviceToHost));
+  return {(int64_t)v[0], (int64_t)v[1]};
 }
 
 // ------------------------------------------------------------------- allreduce
@@ -338,6 +354,7 @@ static float scale_for(const c10d::ReduceOp& op, int n) {
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allreduce(std::vector<at::Tensor>& tensors, const c10d::AllreduceOptions& opts) {
+  NvtxRange nvtx_range("stragglar::allreduce");
   TORCH_CHECK(tensors.size() == 1, "stragglar backend takes one tensor per rank");
   check_contiguous(tensors[0]);
   std::lock_guard<std::mutex> lk(mu_);
@@ -349,6 +366,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allreduce(std::vector<at::
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allreduce_ex(at::Tensor& tensor, bool average, std::optional<at::ScalarType> comm_dtype) {
+  NvtxRange nvtx_range("stragglar::allreduce_ex");
   check_contiguous(tensor);
   std::lock_guard<std::mutex> lk(mu_);
   Side& s = side(tensor);
@@ -393,6 +411,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::reduce(std::vector<at::Ten
 
 // --------------------------------------------------- staged data-movement ops
 c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::broadcast(std::vector<at::Tensor>& tensors, const c10d::BroadcastOptions& opts) {
+  NvtxRange nvtx_range("stragglar::broadcast");
   TORCH_CHECK(tensors.size() == 1, "stragglar backend takes one tensor per rank");
   check_contiguous(tensors[0]);
   std::lock_guard<std::mutex> lk(mu_);
@@ -414,6 +433,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::broadcast(std::vector<at::
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::_allgather_base(at::Tensor& output, at::Tensor& input, const c10d::AllgatherOptions&) {
+  NvtxRange nvtx_range("stragglar::allgather");
   check_contiguous(output); check_contiguous(input);
   const int n = getSize();
   TORCH_CHECK(output.nbytes() == input.nbytes() * n, "all_gather output must be world_size times the input");
@@ -465,6 +485,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allgather_into_tensor_coal
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::_reduce_scatter_base(at::Tensor& output, at::Tensor& input, const c10d::ReduceScatterOptions& opts) {
+  NvtxRange nvtx_range("stragglar::reduce_scatter");
   check_contiguous(output); check_contiguous(input);
   const int n = getSize(), me = getRank();
   TORCH_CHECK(input.numel() == output.numel() * n, "reduce_scatter input must be world_size times the output");
@@ -611,6 +632,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::alltoall(std::vector<at::T
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::barrier(const c10d::BarrierOptions& opts) {
+  NvtxRange nvtx_range("stragglar::barrier");
   std::lock_guard<std::mutex> lk(mu_);
   bool cuda = cuda_.t != nullptr;
   int device = cuda_.device;
@@ -778,4 +800,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("check_status", [](const c10::intrusive_ptr<c10d::Backend>& b, bool cuda) { return cast(b)->check_status(cuda); },
         py::arg("backend"), py::arg("cuda") = true, py::call_guard<py::gil_scoped_release>());
   m.def("launches", [](const c10::intrusive_ptr<c10d::Backend>& b) { return cast(b)->launches(); });
+  m.def("last_trace", [](const c10::intrusive_ptr<c10d::Backend>& b) { return cast(b)->last_trace(); },
+        py::call_guard<py::gil_scoped_release>());
 }

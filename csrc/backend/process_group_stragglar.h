@@ -122,6 +122,10 @@ class ProcessGroupStragglar : public c10d::Backend {
   // (a SarStatus; 0 = ok), clearing a recorded failure.
   int64_t check_status(bool cuda);
   int64_t launches() const { return launches_; }   // kernels of this library launched so far
+  // %globaltimer stamps (ns) of the last collective kernel of this rank: when it arrived and
+  // when it left.  Their difference is the time the rank spent inside the collective; the
+  // persistent straggler is the rank that spends the least (it arrives last and waits for nobody).
+  std::pair<int64_t, int64_t> last_trace();
 
  private:
   struct Side {   // per device type

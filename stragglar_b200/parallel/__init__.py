@@ -103,6 +103,49 @@ def launches(device="cuda", group=None) -> int:
     return _ext().launches(backend_of(device, group))
 
 
+def last_collective_ms(device="cuda", group=None) -> float:
+    """Device time this rank spent inside its last collective kernel
+    (arrival to exit, from %globaltimer stamps written by the kernel)."""
+    a, b = _ext().last_trace(backend_of(device, group))
+    return max(0.0, (b - a) / 1e6)
+
+
+class StragglerMonitor:
+    """Finds the persistent straggler at run time and re-labels the schedule.
+
+    Call :meth:`step` once per training step on every rank (after the
+    gradient AllReduces).  Every rank contributes the time it spent inside its
+    last collective; the rank with the smallest time arrived last -- the rule of
+    the reference's offline analysis (motivation/log_proc.ipynb), applied over
+    a sliding window by :class:`stragglar_b200.detect.OnlineDetector`.  When a
+    rank has been the straggler in ``threshold`` of the last ``window`` steps
+    and differs from the current choice, ``set_straggler`` is applied on all
+    ranks at the same step (every rank sees the same gathered times)."""
+
+    def __init__(self, window: int = 20, threshold: float = 0.8, device="cuda", group=None):
+        import torch.distributed as dist
+        from ..detect import OnlineDetector
+        self.device, self.group = device, group
+        self.detector = OnlineDetector(dist.get_world_size(group), window=window, threshold=threshold)
+        self.changes = 0
+
+    def step(self):
+        import torch
+        import torch.distributed as dist
+        world = dist.get_world_size(self.group)
+        mine = torch.tensor([last_collective_ms(self.device, self.group)], device=self.device)
+        allv = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allv, mine, group=self.group)
+        self.detector.update([float(v.item()) for v in allv])
+        rec = self.detector.recommendation()
+        cur = get_straggler(self.device, self.group)
+        cur = world - 1 if cur < 0 else cur
+        if rec is not None and rec != cur:
+            set_straggler(rec, self.device, self.group)
+            self.changes += 1
+        return rec
+
+
 # ------------------------------------------------------------------ DDP hooks
 def fused_avg_hook(state, bucket):
     """DDP communication hook: AllReduce the gradient bucket with the division

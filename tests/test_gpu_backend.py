@@ -144,3 +144,31 @@ def test_single_process_communicator_over_nvlink(path):
         if delay:
             assert max(ms) >= 2.0
     comm.close()
+
+
+def _monitor(rank, world):
+    import stragglar_b200.parallel as sp
+    from stragglar_b200 import ops
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    x = sp.empty_symmetric(1 << 20, device=dev)
+    x.fill_(1.0)
+    mon = sp.StragglerMonitor(window=5, threshold=0.8, device=dev)
+    late = 0   # not the default straggler (the last rank)
+    for _ in range(6):
+        dist.barrier()
+        if rank == late:
+            ops.delay(4.0)
+        dist.all_reduce(x, op=dist.ReduceOp.AVG)
+        mon.step()
+    assert sp.get_straggler(dev) == late and mon.changes == 1
+    # the re-labelled schedule still reduces correctly
+    y = torch.full((4099,), float(rank + 1), device=dev)
+    dist.all_reduce(y)
+    assert float(y[0]) == sum(range(1, world + 1))
+    assert sp.check_status(dev) == 0
+
+
+@pytest.mark.multigpu
+def test_straggler_monitor_relabels_the_schedule():
+    run_ranks(min(torch.cuda.device_count(), 4) // 2 * 2, _monitor)
