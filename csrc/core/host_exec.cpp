@@ -120,9 +120,23 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   };
 
   const size_t nrounds = t.round_begin.empty() ? 0 : t.round_begin.size() - 1;
+  uint32_t table_lanes = 1;
+  for (const SarOp& op : t.ops) if (op.lane) table_lanes = 2;
+  uint32_t lanes, lane, lblock, lnblocks;
+  sar_lane_of_block((uint32_t)block, (uint32_t)nblocks, table_lanes, &lanes, &lane, &lblock, &lnblocks);
+  const int block_all = block, nblocks_all = nblocks;
+  block = (int)lblock; nblocks = (int)lnblocks;   // from here on: position inside the lane
   uint64_t item_base = 0;
   for (size_t ri = 0; ri < nrounds && status == SAR_OK; ++ri) {
-    const uint32_t ob = t.round_begin[ri], oe = t.round_begin[ri + 1], m = oe - ob;
+    uint32_t ob = t.round_begin[ri], oe = t.round_begin[ri + 1];
+    if (lanes == 2) {
+      // the round's ops are sorted by lane: lane 0 is a prefix, lane 1 the rest
+      uint32_t split = ob;
+      while (split < oe && t.ops[split].lane == 0) ++split;
+      if (lane == 0) oe = split; else ob = split;
+    }
+    const uint32_t m = oe - ob;
+    if (m == 0) continue;
     uint32_t max_tiles = 0;
     for (uint32_t o = ob; o < oe; ++o) max_tiles = std::max(max_tiles, sar_op_tiles(g, t.ops[o]));
     const uint64_t items = (uint64_t)max_tiles * m;
@@ -177,8 +191,9 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
     item_base += items;
   }
   // the last block of this rank to finish announces the exit and waits for every peer's
+  (void)block_all;
   uint32_t done = ctrl_word(me, 3)->fetch_add(1, std::memory_order_acq_rel) + 1;
-  if (done == (uint32_t)nblocks) {
+  if (done == (uint32_t)nblocks_all) {
     ctrl_word(me, 3)->store(0, std::memory_order_relaxed);
     if (status == SAR_OK && !ctrl_word(me, 2)->load(std::memory_order_relaxed)) {
       ctrl_word(me, 1)->store(l.epoch_base, std::memory_order_release);

@@ -329,10 +329,20 @@ bool default_push_copies() {
   return true;
 }
 
+bool default_two_lanes() {
+  const char* v = getenv("STRAGGLAR_LANES");
+  if (v && *v) return atoi(v) >= 2;
+  return true;
+}
+
 static Plan plan_by_name_impl(const std::string& alg, int n, bool prephase, const Schedule* sched);
 Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* sched) {
   Plan p = plan_by_name_impl(alg, n, prephase, sched);
   p.push_copies = default_push_copies();
+  bool has_exchange = false;
+  for (const auto& s : p.steps) has_exchange |= s.kind == StepKind::Exchange;
+  p.two_lanes = has_exchange && default_two_lanes();
+  p.split_copies = has_exchange;
   return p;
 }
 
@@ -483,20 +493,25 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
       op.local_ver = (uint8_t)ver(s.dst);
       op.post_ver = (uint8_t)(ver(s.dst) + 1);
       if (s.kind == StepKind::Copy) {
-        if (plan.push_copies) {
-          // executed by the source: it waits for its own slot (local_ver), for the destination
-          // slot's current version (src_ver) and stores into the destination
-          SarOp po = op;
-          po.kind = SAR_PUSH;
-          po.src[0] = (uint8_t)l2p[s.dst];
-          po.src_ver[0] = (uint8_t)ver(s.dst);
-          po.local_ver = (uint8_t)ver(s.srcs[0]);
-          po.post_ver = 0;
-          po.push_ver = (uint8_t)(ver(s.dst) + 1);
-          ops[s.srcs[0]].push_back(po);
-        } else {
-          op.kind = SAR_COPY;
-          ops[s.dst].push_back(op);
+        const int nparts = plan.split_copies ? 2 : 1;
+        for (int part = 0; part < nparts; ++part) {
+          SarOp co = op;
+          co.part = (uint8_t)part; co.parts = (uint8_t)nparts;
+          co.lane = plan.two_lanes ? 1 : 0;
+          if (plan.push_copies) {
+            // executed by the source: it waits for its own slot (local_ver), for the destination
+            // slot's current version (src_ver) and stores into the destination
+            co.kind = SAR_PUSH;
+            co.src[0] = (uint8_t)l2p[s.dst];
+            co.src_ver[0] = (uint8_t)ver(s.dst);
+            co.local_ver = (uint8_t)ver(s.srcs[0]);
+            co.post_ver = 0;
+            co.push_ver = (uint8_t)(ver(s.dst) + 1);
+            ops[s.srcs[0]].push_back(co);
+          } else {
+            co.kind = SAR_COPY;
+            ops[s.dst].push_back(co);
+          }
         }
         out.chunks_in[l2p[s.dst]] += 1; out.chunks_out[l2p[s.srcs[0]]] += 1;
       } else if (s.kind == StepKind::Reduce) {
@@ -585,6 +600,10 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
       }
       if (!done) merged.push_back(op);
     }
+    // within a round, lane 0 ops first: every (round, lane) is one contiguous range
+    std::stable_sort(merged.begin(), merged.end(), [](const SarOp& a, const SarOp& b) {
+      return a.round != b.round ? a.round < b.round : a.lane < b.lane;
+    });
     ops[lr] = merged;
   }
   for (int pr = 0; pr < np; ++pr) out.ranks[pr].round_begin.assign(1, 0);

@@ -65,6 +65,9 @@ struct Plan {
   std::vector<int> participants;  // ranks whose result is checked
   Expect expect = Expect::AllReduce;
   bool push_copies = false;       // lower Copy steps as SAR_PUSH (executed by the source) instead of SAR_COPY
+  bool two_lanes = false;         // forwarding ops go to lane 1 (their own blocks), the rest to lane 0
+  bool split_copies = false;      // forward a chunk as two half-chunk ops, interleaved tile by tile, so that
+                                  // forwarding follows both halves of a straggler matching as they are produced
   int num_rounds() const;
 };
 
@@ -84,6 +87,8 @@ Plan plan_rsag(int n);                      // one-shot reduce-scatter + all-gat
 Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* sched = nullptr);
 // How Copy steps are lowered unless a plan says otherwise: STRAGGLAR_COPY=pull|push (default push).
 bool default_push_copies();
+// STRAGGLAR_LANES=1|2 (default 2): whether plans with straggler matchings use a forwarding lane.
+bool default_two_lanes();
 
 struct RankTable {
   std::vector<SarOp> ops;

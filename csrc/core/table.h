@@ -73,7 +73,8 @@ struct SarOp {
   uint8_t local_ver;   // version the own slot must have before it is read or overwritten
   uint8_t post_ver;    // version of the own slot after this op
   uint8_t push_ver;    // REDUCE_PUSH / PUSH: version of the peer slot after this op
-  uint8_t pad[2];
+  uint8_t lane;        // 0 or 1: which group of blocks executes the op (see sar_lane_of_block)
+  uint8_t pad;
   uint8_t src[SAR_MAX_RANKS];      // peer ranks (physical)
   uint8_t src_ver[SAR_MAX_RANKS];  // version needed of each peer's slot (PUSH: the version it replaces)
 };
@@ -125,6 +126,20 @@ SAR_HD uint32_t sar_op_tiles(const SarGeom& g, const SarOp& op) {
 }
 SAR_HD uint32_t sar_flag_index(const SarGeom& g, uint32_t chunk, uint32_t tile) {
   return chunk * g.tiles_per_chunk + tile;
+}
+// Lanes.  A table may put its ops in two lanes (0: reductions and straggler
+// matchings, 1: forwarding of finished chunks).  The blocks of a rank are then
+// split between the lanes and every lane walks its own ops in round order, so
+// that forwarding overlaps the matchings instead of queueing behind them in
+// the same blocks.  With a single block (or a one-lane table) there is one
+// lane that walks every op.
+SAR_HD void sar_lane_of_block(uint32_t block, uint32_t nblocks, uint32_t table_lanes, uint32_t* lanes,
+                              uint32_t* lane, uint32_t* lane_block, uint32_t* lane_nblocks) {
+  const uint32_t L = (table_lanes >= 2 && nblocks >= 2) ? 2u : 1u;
+  *lanes = L;
+  *lane = block % L;
+  *lane_block = block / L;
+  *lane_nblocks = (nblocks - *lane + L - 1) / L;
 }
 // wrap-safe "flag has reached target"
 SAR_HD bool sar_reached(uint32_t flag, uint32_t target) { return (int32_t)(flag - target) >= 0; }

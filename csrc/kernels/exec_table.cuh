@@ -184,12 +184,13 @@ struct OpGeom {
 struct RoundGeom { uint32_t op_begin, m, max_tiles, pad; };
 struct TableGeom {
   OpGeom op[SAR_MAX_OPS];
-  RoundGeom round[SAR_MAX_ROUNDS];
+  RoundGeom round[2][SAR_MAX_ROUNDS];   // per lane
   uint32_t num_rounds;
+  uint32_t lanes;                       // lanes in effect for this launch (1 or 2)
 };
 
 // All threads of the block; ends with a block barrier.
-__device__ void resolve_table(const SarLaunchParams& P, TableGeom& G) {
+__device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t nblocks) {
   const uint32_t nrounds = P.num_rounds < SAR_MAX_ROUNDS ? P.num_rounds : SAR_MAX_ROUNDS;
   const uint32_t nops = nrounds ? P.round_begin[nrounds] : 0;
   for (uint32_t o = threadIdx.x; o < nops && o < SAR_MAX_OPS; o += blockDim.x) {
@@ -202,14 +203,26 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G) {
     G.op[o].ntiles = t1 - t0;
     G.op[o].tile0 = t0;
   }
+  if (threadIdx.x == 0) {
+    uint32_t table_lanes = 1;
+    for (uint32_t o = 0; o < nops && o < SAR_MAX_OPS; ++o) if (P.ops[o].lane) table_lanes = 2;
+    uint32_t lanes, lane, lb, lnb;
+    sar_lane_of_block(0, nblocks, table_lanes, &lanes, &lane, &lb, &lnb);
+    G.lanes = lanes;
+    G.num_rounds = nrounds;
+  }
   __syncthreads();
   for (uint32_t r = threadIdx.x; r < nrounds; r += blockDim.x) {
     const uint32_t ob = P.round_begin[r], oe = P.round_begin[r + 1];
-    uint32_t mx = 0;
-    for (uint32_t o = ob; o < oe; ++o) mx = G.op[o].ntiles > mx ? G.op[o].ntiles : mx;
-    G.round[r].op_begin = ob; G.round[r].m = oe - ob; G.round[r].max_tiles = mx;
+    uint32_t split = oe;                  // one lane: every op of the round
+    if (G.lanes == 2) { split = ob; while (split < oe && P.ops[split].lane == 0) ++split; }
+    for (uint32_t l = 0; l < 2; ++l) {
+      const uint32_t b = l == 0 ? ob : split, e = l == 0 ? split : oe;
+      uint32_t mx = 0;
+      for (uint32_t o = b; o < e; ++o) mx = G.op[o].ntiles > mx ? G.op[o].ntiles : mx;
+      G.round[l][r].op_begin = b; G.round[l][r].m = e - b; G.round[l][r].max_tiles = mx;
+    }
   }
-  if (threadIdx.x == 0) G.num_rounds = nrounds;
   __syncthreads();
 }
 
@@ -217,18 +230,21 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G) {
 struct ItemWalker {
   const SarLaunchParams* P;
   const TableGeom* G;
-  uint32_t block, nblocks;
+  uint32_t block, nblocks;   // position and size inside the block's lane
+  uint32_t lane;
   uint32_t ri;            // current round index
   uint32_t ob, m, items, k, base_mod;
   __device__ void init(const SarLaunchParams* p, const TableGeom* g, uint32_t b, uint32_t nb) {
-    P = p; G = g; block = b; nblocks = nb; ri = 0; base_mod = 0;
+    P = p; G = g; ri = 0; base_mod = 0;
+    uint32_t lanes;
+    sar_lane_of_block(b, nb, g->lanes, &lanes, &lane, &block, &nblocks);
     load_round();
   }
   __device__ void load_round() {
     while (ri < G->num_rounds) {
-      ob = G->round[ri].op_begin;
-      m = G->round[ri].m;
-      items = G->round[ri].max_tiles * m;
+      ob = G->round[lane][ri].op_begin;
+      m = G->round[lane][ri].m;
+      items = G->round[lane][ri].max_tiles * m;
       k = (block + nblocks - base_mod) % nblocks;
       if (k < items) return;
       base_mod = (base_mod + items) % nblocks;
@@ -482,7 +498,7 @@ __device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t
   __shared__ Item s_item;
   __shared__ int s_state;   // 1: item ready, 0: table exhausted, -1: a wait failed
   WaitCtx w = enter_collective(P, block);
-  resolve_table(P, G);
+  resolve_table(P, G, nblocks);
   ItemWalker walk;
   uint32_t arrived = 1u << P.rank;
   if (threadIdx.x == 0) walk.init(&P, &G, block, nblocks);
@@ -634,7 +650,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  resolve_table(P, S.geom);   // ends with a block barrier
+  resolve_table(P, S.geom, nblocks);   // ends with a block barrier
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer

@@ -30,7 +30,7 @@ MAX_RANKS = 16
 VER_STRIDE = 32
 OP_DTYPE = np.dtype([
     ("kind", "u1"), ("flags", "u1"), ("round", "u1"), ("chunk", "u1"), ("part", "u1"), ("parts", "u1"),
-    ("nsrc", "u1"), ("local_ver", "u1"), ("post_ver", "u1"), ("push_ver", "u1"), ("pad", "u1", (2,)),
+    ("nsrc", "u1"), ("local_ver", "u1"), ("post_ver", "u1"), ("push_ver", "u1"), ("lane", "u1"), ("pad", "u1"),
     ("src", "u1", (MAX_RANKS,)), ("src_ver", "u1", (MAX_RANKS,)),
 ])
 COPY, REDUCE, REDUCE_PUSH, PUSH = 0, 1, 2, 3
