@@ -249,8 +249,11 @@ def main() -> int:
         dist.all_gather(allms, ms)
         return max(float(m.item()) for m in allms) / steps, launches
 
-    with ClockSampler(local) as cs:
-        ms_step, launches = timed(device_step, args.steps)
+    # clocks are sampled from here to the end of the end-to-end region (nvidia-smi answers in
+    # ~100 ms, the device-timed region alone may be shorter than that)
+    cs = ClockSampler(local)
+    cs.__enter__()
+    ms_step, launches = timed(device_step, args.steps)
     st = sp.check_status(dev)
     if st:
         raise RuntimeError("collective failed: " + status_string(st))
@@ -284,6 +287,7 @@ def main() -> int:
                "d2h_bytes_per_step": back * esize,
                "path": "pinned host -> symmetric device tensor -> dist.all_reduce(op=AVG) -> 4 KiB of the result back"}
 
+    cs.__exit__(None, None, None)
     prog_post = compile_program(args.alg, world, prephase=(delay_ms == 0), straggler=straggler)
     link_bytes = prog_post.link_bytes(nbytes)
     roof_ms = link_bytes / 770e9 * 1e3 if world > 1 else 2 * nbytes / 6532.5e9 * 1e3
