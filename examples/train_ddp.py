@@ -49,6 +49,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--tiny", action="store_true", help="a 2-layer model for smoke tests")
     ap.add_argument("--lr", type=float, default=5e-5)
+    ap.add_argument("--auto-straggler", action="store_true",
+                    help="find the late rank at run time (StragglerMonitor) instead of trusting --straggler")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -85,6 +87,9 @@ def main() -> int:
         print(f"model: {nparams / 1e9:.3f} B parameters, {grad_bytes / 2**20:.0f} MiB of gradients per step, "
               f"backend {args.backend}, straggler rank {straggler} (+{args.delay_ms} ms)", flush=True)
 
+    monitor = None
+    if args.backend == "stragglar" and args.auto_straggler:
+        monitor = sp.StragglerMonitor(window=5, threshold=0.8, device=dev)
     tokens_per_step = world * args.micro_batch * args.seq_len
     times = []
     for step in range(args.warmup + args.steps):
@@ -117,6 +122,8 @@ def main() -> int:
         t = torch.tensor([iter_ms], device=dev)
         allt = [torch.zeros_like(t) for _ in range(world)]
         dist.all_gather(allt, t)
+        if monitor is not None:
+            monitor.step()
         if step >= args.warmup:
             times.append(max(float(a.item()) for a in allt))
     if args.backend == "stragglar":

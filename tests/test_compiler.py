@@ -169,3 +169,35 @@ def test_property_any_size_any_straggler(n, count, straggler, alg, tile, blocks)
     prog, bufs, want = _run(alg, n, count, straggler=straggler, blocks=blocks, tile=tile)
     for b in bufs:
         np.testing.assert_allclose(b, want, atol=2e-5)
+
+
+def test_forwarding_lane_and_merged_pushes(monkeypatch):
+    monkeypatch.setenv("STRAGGLAR_COPY", "push")
+    monkeypatch.setenv("STRAGGLAR_LANES", "2")
+    t = sc.compile_table("stragglar_a2a", 8)
+    ops = t.ranks[0].ops
+    kinds = [(int(o["kind"]), int(o["round"]), int(o["lane"]), int(o["nsrc"]), int(o["part"]), int(o["parts"])) for o in ops]
+    # pre-phase reduce (6 peers), the rank's half of its matching, then its final chunk pushed to the
+    # six other non-stragglers as two interleaved half-chunk ops in the forwarding lane
+    assert kinds == [(sc.REDUCE, 0, 0, 6, 0, 1), (sc.REDUCE_PUSH, 1, 0, 1, 0, 2),
+                     (sc.PUSH, 2, 1, 6, 0, 2), (sc.PUSH, 2, 1, 6, 1, 2)]
+    # the straggler only has matchings: no forwarding lane, all of its blocks serve them
+    assert all(int(o["lane"]) == 0 and int(o["kind"]) == sc.REDUCE_PUSH for o in t.ranks[7].ops)
+    # within a round lane 0 comes first
+    s = sc.compile_table("stragglar", 8)
+    for r in s.ranks:
+        key = [(int(o["round"]), int(o["lane"])) for o in r.ops]
+        assert key == sorted(key)
+    # ring has no matchings: one lane, whole-chunk ops
+    assert all(int(o["lane"]) == 0 and int(o["parts"]) == 1 for r in sc.compile_table("ring", 8).ranks for o in r.ops)
+
+
+@pytest.mark.parametrize("copy,lanes", [("pull", "1"), ("pull", "2"), ("push", "1"), ("push", "2")])
+def test_every_lowering_gives_the_same_sum(monkeypatch, copy, lanes):
+    monkeypatch.setenv("STRAGGLAR_COPY", copy)
+    monkeypatch.setenv("STRAGGLAR_LANES", lanes)
+    for alg in ("stragglar", "stragglar_a2a", "direct"):
+        for blocks in (1, 2, 5):
+            prog, bufs, want = _run(alg, 8, 3001, blocks=blocks, tile=32)
+            for b in bufs:
+                np.testing.assert_allclose(b, want, atol=1e-5, err_msg=f"{alg} {copy} {lanes} {blocks}")
