@@ -29,6 +29,7 @@ void sar_program_free(sar_program* p);
 int sar_program_num_phases(const sar_program* p);
 const sar_table* sar_program_phase(const sar_program* p, int i);
 int sar_table_channel(const sar_table* t);
+int sar_table_blocks_hint(const sar_table* t);   // 0, or the largest block count per rank worth using
 uint32_t sar_table_participants(const sar_table* t);
 int sar_table_nranks(const sar_table* t);
 int sar_table_num_chunks(const sar_table* t);

@@ -323,25 +323,32 @@ Plan plan_rsag(int n) {
   return p;
 }
 
-bool default_push_copies() {
+// Lowering defaults, from measurements on 8 x B200 (1 GiB, fp32, after the straggler's arrival):
+//   stragglar      pulled copies, one lane     2.67 ms   (pushed 3.23, pushed + forwarding lane 3.42)
+//   stragglar_a2a  pushed copies, two lanes    2.00 ms   (one lane 2.93, pulled 3.01)
+//   ring / rsag    pushed copies               2.78 / 2.86 ms (pulled 2.94 / 2.90)
+//   direct         pulled copies, one lane     4.42 ms   (pushed 4.53)
+// STRAGGLAR_COPY=pull|push and STRAGGLAR_LANES=1|2 override them.
+static bool push_default_for(const std::string& alg) {
   const char* v = getenv("STRAGGLAR_COPY");
   if (v && *v) return std::string(v) != "pull";
-  return true;
+  return !(alg == "stragglar" || alg == "direct");
 }
-
-bool default_two_lanes() {
+static bool two_lanes_default_for(const std::string& alg) {
   const char* v = getenv("STRAGGLAR_LANES");
   if (v && *v) return atoi(v) >= 2;
-  return true;
+  return alg == "stragglar_a2a";
 }
+bool default_push_copies() { return push_default_for(""); }
+bool default_two_lanes() { return two_lanes_default_for(""); }
 
 static Plan plan_by_name_impl(const std::string& alg, int n, bool prephase, const Schedule* sched);
 Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* sched) {
   Plan p = plan_by_name_impl(alg, n, prephase, sched);
-  p.push_copies = default_push_copies();
+  p.push_copies = push_default_for(alg);
   bool has_exchange = false;
   for (const auto& s : p.steps) has_exchange |= s.kind == StepKind::Exchange;
-  p.two_lanes = has_exchange && default_two_lanes();
+  p.two_lanes = has_exchange && two_lanes_default_for(alg);
   p.split_copies = has_exchange;
   return p;
 }
@@ -569,6 +576,11 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
     i = j;
   }
   if (out.max_version >= (int)SAR_VER_STRIDE) throw CompileError("too many versions of one slot");
+  // Tables whose ranks push one tile to several peers at once run best with fewer blocks
+  // (64 rather than 128 per rank at 1 GiB on 8 x B200: 2.00 ms against 2.64 ms for stragglar_a2a).
+  for (int lr = 0; lr < n; ++lr)
+    for (const SarOp& op : ops[lr])
+      if (op.kind == SAR_PUSH && op.nsrc >= 2) out.blocks_hint = 64;
   // result check
   const uint32_t want = full_mask(n);
   for (int r : plan.participants) {

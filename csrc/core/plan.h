@@ -85,9 +85,8 @@ Plan plan_direct(int n, bool prephase);
 Plan plan_reduce_scatter(int n);            // rank i ends with the sum of chunk i (n chunks)
 Plan plan_rsag(int n);                      // one-shot reduce-scatter + all-gather
 Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* sched = nullptr);
-// How Copy steps are lowered unless a plan says otherwise: STRAGGLAR_COPY=pull|push (default push).
+// Lowering used for algorithms without a measured preference (STRAGGLAR_COPY / STRAGGLAR_LANES override).
 bool default_push_copies();
-// STRAGGLAR_LANES=1|2 (default 2): whether plans with straggler matchings use a forwarding lane.
 bool default_two_lanes();
 
 struct RankTable {
@@ -103,6 +102,7 @@ struct Compiled {
   int num_chunks = 0;
   int max_version = 0;
   int num_rounds = 0;
+  int blocks_hint = 0;    // upper bound of the blocks per rank this table runs best with (0: none)
   std::vector<RankTable> ranks;          // by physical rank
   std::vector<int> logical_to_physical;
   // per-rank traffic in chunks (for rooflines): chunks read from peers, chunks written to peers

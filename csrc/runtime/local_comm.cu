@@ -188,7 +188,10 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
     const uint32_t parts = sar_table_participants(t);
     const uint32_t nch = (uint32_t)sar_table_num_chunks(t);
     c->epoch[ch] += SAR_VER_STRIDE;
-    const uint32_t tile_elems = sar_pick_tile_elems(count, esize, nch, (uint32_t)blocks, 2048, tile_max);
+    int pblocks = blocks;   // this phase's block count: the table may ask for fewer
+    const int hint = sar_table_blocks_hint(t);
+    if (o->blocks <= 0 && !c->emulate && hint > 0 && hint < pblocks) pblocks = hint;
+    const uint32_t tile_elems = sar_pick_tile_elems(count, esize, nch, (uint32_t)pblocks, 2048, tile_max);
     SarGeom g = sar::make_geom(count, esize, nch, tile_elems);
     if ((uint64_t)g.tiles_per_chunk * g.num_chunks > SAR_FLAG_CAPACITY) {
       if (err) snprintf(err, errlen, "buffer too large for the flag array");
@@ -219,9 +222,9 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       CK(cudaSetDevice(c->ranks[0].dev));
       CK(cudaMemcpyAsync(c->d_params, hp.data(), sizeof(SarLaunchParams) * n, cudaMemcpyHostToDevice, c->ranks[0].stream));
       // the copy is from pageable memory: it has completed with respect to the host buffer on return
-      cudaError_t e = (cudaError_t)sar_cuda_launch_emulated(c->d_params, n, dtype, path, blocks, o->threads, c->ranks[0].stream);
+      cudaError_t e = (cudaError_t)sar_cuda_launch_emulated(c->d_params, n, dtype, path, pblocks, o->threads, c->ranks[0].stream);
       if (e != cudaSuccess) {
-        if (err) snprintf(err, errlen, "emulated launch (%d ranks x %d blocks): %s", n, blocks, cudaGetErrorString(e));
+        if (err) snprintf(err, errlen, "emulated launch (%d ranks x %d blocks): %s", n, pblocks, cudaGetErrorString(e));
         return (int)e;
       }
     } else {
@@ -230,7 +233,7 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
         Rank& rk = c->ranks[r];
         CK(cudaSetDevice(rk.dev));
         if (delay_ns && delay_ns[r] && !delayed[r]) { CK((cudaError_t)sar_cuda_delay(delay_ns[r], rk.stream)); delayed[r] = true; }
-        CK((cudaError_t)sar_cuda_launch(&hp[r], path, blocks, o->threads, rk.stream));
+        CK((cudaError_t)sar_cuda_launch(&hp[r], path, pblocks, o->threads, rk.stream));
       }
     }
   }
