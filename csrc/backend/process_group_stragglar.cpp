@@ -666,8 +666,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::send(std::vector<at::Tenso
   auto w = begin(s, c10d::OpType::SEND, {});
   char* p = (char*)tensors[0].data_ptr();
   const size_t bytes = tensors[0].nbytes(), piece = t.staging_bytes();
-  static thread_local std::map<std::pair<const void*, int>, uint32_t> seqs;
-  uint32_t& seq = seqs[{(const void*)&t, dst}];
+  uint32_t& seq = send_seq_[{t.cuda(), dst}];
   for (size_t off = 0; off < bytes || off == 0; off += piece) {
     const size_t k = std::min(piece, bytes - off);
     copy_local(s, t.data(me) + t.staging_off(), p + off, k);
@@ -702,8 +701,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::recv(std::vector<at::Tenso
   auto w = begin(s, c10d::OpType::RECV, tensors);
   char* p = (char*)tensors[0].data_ptr();
   const size_t bytes = tensors[0].nbytes(), piece = t.staging_bytes();
-  static thread_local std::map<std::pair<const void*, int>, uint32_t> seqs;
-  uint32_t& seq = seqs[{(const void*)&t, src}];
+  uint32_t& seq = recv_seq_[{t.cuda(), src}];
   for (size_t off = 0; off < bytes || off == 0; off += piece) {
     const size_t k = std::min(piece, bytes - off);
     ++seq;
@@ -748,11 +746,11 @@ at::Tensor ProcessGroupStragglar::alloc_symmetric(int64_t numel, at::ScalarType 
                 std::string(v.begin(), v.end()), " but rank ", getRank(), " allocated ", mine,
                 " (every rank must allocate the same sizes in the same order)");
   }
-  Transport* tp = s.t.get();
+  std::shared_ptr<Heap> heap = t.heap();
   auto opts = at::TensorOptions().dtype(dtype);
   opts = cuda ? opts.device(at::kCUDA, (c10::DeviceIndex)device) : opts.device(at::kCPU);
   // the block returns to the heap when the tensor dies; the arena outlives the tensors of a well-formed program
-  return at::from_blob(t.data(getRank()) + off, {numel}, [tp, off](void*) { tp->heap_free(off); }, opts);
+  return at::from_blob(t.data(getRank()) + off, {numel}, [heap, off](void*) { heap->free(off); }, opts);
 }
 
 // -------------------------------------------------------------------- bindings

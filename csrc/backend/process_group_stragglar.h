@@ -155,6 +155,7 @@ class ProcessGroupStragglar : public c10d::Backend {
   std::mutex mu_;
   int64_t launches_ = 0;
   uint64_t alloc_seq_ = 0;
+  std::map<std::pair<bool, int>, uint32_t> send_seq_, recv_seq_;   // (cuda?, peer) -> handshakes so far
 };
 
 }  // namespace sarpg

@@ -30,7 +30,7 @@ Transport::Transport(bool cuda, int device, int rank, int n, size_t data_bytes, 
   data_bytes_ = (data_bytes + 4095) / 4096 * 4096;
   staging_bytes_ = std::min(data_bytes_, (staging_bytes + 4095) / 4096 * 4096);
   total_bytes_ = ArenaLayout::kDataOff + data_bytes_;
-  blocks_.push_back({0, heap_bytes(), false});
+  heap_ = std::make_shared<Heap>(heap_bytes());
   const std::string me = prefix + "/arena/" + std::to_string(rank);
   if (cuda_) {
     SAR_CUDA_CHECK(cudaSetDevice(device));
@@ -103,7 +103,8 @@ int64_t Transport::heap_offset(const void* p, size_t bytes) const {
   return c - lo;
 }
 
-int64_t Transport::heap_alloc(size_t bytes) {
+int64_t Heap::alloc(size_t bytes) {
+  std::lock_guard<std::mutex> lk(mu_);
   bytes = (bytes + 255) / 256 * 256;
   if (bytes == 0) bytes = 256;
   for (size_t i = 0; i < blocks_.size(); ++i) {
@@ -119,7 +120,8 @@ int64_t Transport::heap_alloc(size_t bytes) {
   return -1;
 }
 
-void Transport::heap_free(int64_t off) {
+void Heap::free(int64_t off) {
+  std::lock_guard<std::mutex> lk(mu_);
   for (size_t i = 0; i < blocks_.size(); ++i) {
     if ((int64_t)blocks_[i].off != off || !blocks_[i].used) continue;
     blocks_[i].used = false;

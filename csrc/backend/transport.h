@@ -13,6 +13,8 @@
 
 #include <atomic>
 #include <cstdint>
+#include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -26,6 +28,19 @@ struct ArenaLayout {
   static constexpr size_t kFlagsOff = 4096;
   static constexpr size_t kFlagsBytes = sizeof(uint32_t) * (size_t)SAR_NUM_CHANNELS * SAR_FLAG_CAPACITY;
   static constexpr size_t kDataOff = kFlagsOff + kFlagsBytes;
+};
+
+// Bookkeeping of the symmetric heap.  Shared with the deleters of the tensors handed out, so that a
+// tensor outliving its process group only returns its block to a dead book instead of touching freed memory.
+class Heap {
+ public:
+  explicit Heap(size_t bytes) { blocks_.push_back({0, bytes, false}); }
+  int64_t alloc(size_t bytes);
+  void free(int64_t off);
+ private:
+  struct Block { size_t off, bytes; bool used; };
+  std::vector<Block> blocks_;
+  std::mutex mu_;
 };
 
 class Transport {
@@ -58,8 +73,9 @@ class Transport {
   // offset into the data region if p lies inside this rank's heap, else -1
   int64_t heap_offset(const void* p, size_t bytes) const;
   // symmetric heap: the same call sequence on every rank yields the same offsets
-  int64_t heap_alloc(size_t bytes);
-  void heap_free(int64_t off);
+  int64_t heap_alloc(size_t bytes) { return heap_->alloc(bytes); }
+  void heap_free(int64_t off) { heap_->free(off); }
+  std::shared_ptr<Heap> heap() const { return heap_; }
 
  private:
   bool cuda_;
@@ -69,8 +85,7 @@ class Transport {
   uint32_t epoch_[SAR_NUM_CHANNELS] = {};
   uint32_t barrier_epoch_ = 0;
   std::string shm_name_;
-  struct Block { size_t off, bytes; bool used; };
-  std::vector<Block> blocks_;
+  std::shared_ptr<Heap> heap_;
 };
 
 }  // namespace sarpg
