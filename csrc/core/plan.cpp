@@ -350,6 +350,13 @@ Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* 
   for (const auto& s : p.steps) has_exchange |= s.kind == StepKind::Exchange;
   p.two_lanes = has_exchange && two_lanes_default_for(alg);
   p.split_copies = has_exchange;
+  // Blocks per rank beyond which the collective gets slower (8 x B200, 1 GiB, after the arrival):
+  //   stragglar      48: -, 64: 2.42 ms, 96: 2.62, 128: 2.60
+  //   stragglar_a2a  32: 1.83 ms, 48: 1.83, 64: 2.00, 96: 2.45, 128: 2.64
+  // (more concurrent flows per link only add contention once the link is saturated);
+  // ring / rhd / rsag keep improving up to 128.
+  if (alg == "stragglar") p.blocks_hint = 64;
+  if (alg == "stragglar_a2a") p.blocks_hint = 32;
   return p;
 }
 
@@ -576,11 +583,7 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
     i = j;
   }
   if (out.max_version >= (int)SAR_VER_STRIDE) throw CompileError("too many versions of one slot");
-  // Tables whose ranks push one tile to several peers at once run best with fewer blocks
-  // (64 rather than 128 per rank at 1 GiB on 8 x B200: 2.00 ms against 2.64 ms for stragglar_a2a).
-  for (int lr = 0; lr < n; ++lr)
-    for (const SarOp& op : ops[lr])
-      if (op.kind == SAR_PUSH && op.nsrc >= 2) out.blocks_hint = 64;
+  out.blocks_hint = plan.blocks_hint;
   // result check
   const uint32_t want = full_mask(n);
   for (int r : plan.participants) {

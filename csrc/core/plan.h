@@ -65,6 +65,7 @@ struct Plan {
   std::vector<int> participants;  // ranks whose result is checked
   Expect expect = Expect::AllReduce;
   bool push_copies = false;       // lower Copy steps as SAR_PUSH (executed by the source) instead of SAR_COPY
+  int blocks_hint = 0;            // largest block count per rank worth using (0: no preference)
   bool two_lanes = false;         // forwarding ops go to lane 1 (their own blocks), the rest to lane 0
   bool split_copies = false;      // forward a chunk as two half-chunk ops, interleaved tile by tile, so that
                                   // forwarding follows both halves of a straggler matching as they are produced

@@ -73,7 +73,7 @@ def lib():
             L.sar_host_execute_program.restype = C.c_uint32
             L.sar_host_execute_program.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_uint64, C.c_int, C.c_uint32,
                                                    C.c_float, C.c_int, C.POINTER(C.c_double), C.c_double]
-            for name in ("nranks", "num_chunks", "num_rounds", "max_version", "channel"):
+            for name in ("nranks", "num_chunks", "num_rounds", "max_version", "channel", "blocks_hint"):
                 f = getattr(L, f"sar_table_{name}")
                 f.restype, f.argtypes = C.c_int, [C.c_void_p]
             for name in ("num_ops", "num_round_begin"):
@@ -120,6 +120,7 @@ class Table:
         self.num_rounds = L.sar_table_num_rounds(handle)
         self.max_version = L.sar_table_max_version(handle)
         self.channel = L.sar_table_channel(handle)
+        self.blocks_hint = L.sar_table_blocks_hint(handle)
         self.participants = L.sar_table_participants(handle)
         self.ranks: List[RankTable] = []
         for r in range(self.n):

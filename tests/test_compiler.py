@@ -201,3 +201,10 @@ def test_every_lowering_gives_the_same_sum(monkeypatch, copy, lanes):
             prog, bufs, want = _run(alg, 8, 3001, blocks=blocks, tile=32)
             for b in bufs:
                 np.testing.assert_allclose(b, want, atol=1e-5, err_msg=f"{alg} {copy} {lanes} {blocks}")
+
+
+def test_block_count_hints():
+    assert sc.compile_table("stragglar", 8).blocks_hint == 64
+    assert sc.compile_table("stragglar_a2a", 8).blocks_hint == 32
+    assert sc.compile_table("ring", 8).blocks_hint == 0
+    assert [t.blocks_hint for t in sc.compile_program("direct", 8).phases] == [0, 0]
