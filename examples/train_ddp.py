@@ -31,8 +31,7 @@ from torch.nn.parallel import DistributedDataParallel as DDP
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from stragglar_b200.models import LlamaConfig, LlamaForCausalLM  # noqa: E402
 
-RANK_COLORS = ["\033[91m", "\033[92m", "\033[93m", "\033[94m", "\033[95m", "\033[96m"]
-RESET = "\033[0m"
+from stragglar_b200.utils.logfmt import format_step  # noqa: E402
 
 
 def main() -> int:
@@ -80,7 +79,6 @@ def main() -> int:
     opt = torch.optim.AdamW(ddp.parameters(), lr=args.lr)
     sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: min(1.0, (s + 1) / 50))
     gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
-    color = RANK_COLORS[rank % len(RANK_COLORS)]
     nparams = sum(p.numel() for p in model.parameters())
     grad_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
     if rank == 0:
@@ -116,9 +114,8 @@ def main() -> int:
         torch.cuda.synchronize()
         iter_ms = ev[0].elapsed_time(ev[3])
         fwd, bwd = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
-        print(f"{color}Rank {rank} | Step {step} | Forward Time: {fwd:.2f} ms | Backward Time: {bwd:.2f} ms  | "
-              f"Loss: {loss_val:.4f} | Iteration Time: {iter_ms:.2f} ms | AR Time: {bwd:.2f} ms | "
-              f"AR Buffer Size: {grad_bytes / 1024:.2f} KB{RESET}\n", flush=True)
+        # the gradient AllReduces overlap the backward pass, so "AR Time" is the backward time
+        print(format_step(rank, step, fwd, bwd, loss_val, iter_ms, bwd, grad_bytes) + "\n", flush=True)
         t = torch.tensor([iter_ms], device=dev)
         allt = [torch.zeros_like(t) for _ in range(world)]
         dist.all_gather(allt, t)

@@ -94,3 +94,18 @@ def test_online_detector():
     a = detect.OnlineDetector(3, window=2, arrival=True)
     a.update([0.1, 0.2, 5.0]); a.update([0.1, 0.3, 7.0])
     assert a.recommendation() == 2
+
+
+def test_log_line_round_trip_and_detection():
+    from stragglar_b200.utils.logfmt import format_step, parse_step
+    line = format_step(2, 7, 1499.21, 3032.68, 5.3932, 4815.84, 117.94, 12850999296)
+    rec = parse_step(line)
+    assert rec["rank"] == 2 and rec["step"] == 7 and rec["ar_ms"] == 117.94 and rec["forward_ms"] == 1499.21
+    table = detect.parse_ar_times([line + "\n", format_step(0, 7, 1.0, 2.0, 5.0, 9.0, 141.09, 1024) + "\n"])
+    assert table == {7: {2: 117.94, 0: 141.09}}
+
+
+def test_env_report_runs_without_a_gpu():
+    from stragglar_b200.utils import env_check
+    info = env_check.report()
+    assert "torch" in info and isinstance(info["gpus"], list)
