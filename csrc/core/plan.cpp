@@ -355,8 +355,9 @@ Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* 
   //   stragglar_a2a  32: 1.83 ms, 48: 1.83, 64: 2.00, 96: 2.45, 128: 2.64
   // (more concurrent flows per link only add contention once the link is saturated);
   // ring / rhd / rsag keep improving up to 128.
-  if (alg == "stragglar") p.blocks_hint = 64;
-  if (alg == "stragglar_a2a") p.blocks_hint = 32;
+  // With one or two ranks there is a single flow per link and more blocks keep helping.
+  if (alg == "stragglar" && n >= 4) p.blocks_hint = 64;
+  if (alg == "stragglar_a2a" && n >= 4) p.blocks_hint = 32;
   return p;
 }
 

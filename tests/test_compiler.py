@@ -207,4 +207,5 @@ def test_block_count_hints():
     assert sc.compile_table("stragglar", 8).blocks_hint == 64
     assert sc.compile_table("stragglar_a2a", 8).blocks_hint == 32
     assert sc.compile_table("ring", 8).blocks_hint == 0
+    assert sc.compile_table("stragglar", 2).blocks_hint == 0 and sc.compile_table("stragglar", 1).blocks_hint == 0
     assert [t.blocks_hint for t in sc.compile_program("direct", 8).phases] == [0, 0]
