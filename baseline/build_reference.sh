@@ -8,7 +8,7 @@
 # The reference's c10d backend (implementation/custom_backend) installs with
 #   pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <copy of custom_backend>
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:?usage: build_reference.sh <path to a checkout of arjundevraj/stragglar>}
 OUT="$(cd "$(dirname "$0")" && pwd)/_ref"
 mkdir -p "$OUT"
 ARCH="-gencode arch=compute_100,code=sm_100"

@@ -5,7 +5,8 @@
 // n for ring / halving-doubling); a chunk is cut into tiles of `tile_elems`
 // elements.  Every op works on one chunk (or on one of `parts` equal tile
 // ranges of it) and is executed tile by tile by the rank that owns the table.
-// All data movement is a *pull*: the executing rank loads from peer memory.
+// Reductions are *pulls* (the executing rank loads its peers' tiles), which makes
+// them safe in place without temporary buffers; copies are pulls or pushes.
 //
 //   SAR_COPY         own[chunk] = peer[chunk]
 //   SAR_REDUCE       own[chunk] = (own[chunk] +) sum over nsrc peers
@@ -144,18 +145,10 @@ SAR_HD void sar_lane_of_block(uint32_t block, uint32_t nblocks, uint32_t table_l
 // wrap-safe "flag has reached target"
 SAR_HD bool sar_reached(uint32_t flag, uint32_t target) { return (int32_t)(flag - target) >= 0; }
 
-// Work items of one rank.  The ops of one round are interleaved tile by tile
-// (item k of a round with m ops is tile k/m of op k%m, skipping ops that have
-// run out of tiles), and rounds follow one another.  Block b of G executes the
-// items b, b+G, b+2G, ... in this order, which keeps a rank's blocks on the
-// same round and lets every op of a round progress at the same rate.
-struct SarRoundSpan {
-  uint16_t op_begin, op_end;  // ops [op_begin, op_end) belong to this round
-  uint32_t max_tiles;         // max tiles over these ops
-  uint64_t item_begin;        // first item index of the round (dense numbering below)
-};
-// Items are numbered densely per round as k = tile * m + j (j = op within the
-// round); an item whose op has fewer tiles than `tile` is void and skipped.
-SAR_HD uint64_t sar_round_items(const SarRoundSpan& r) {
-  return (uint64_t)r.max_tiles * (uint32_t)(r.op_end - r.op_begin);
-}
+// Work items of one rank.  The ops of one round (of one lane) are interleaved
+// tile by tile: item k of a round with m ops is tile k/m of op k%m (items whose
+// op has run out of tiles are skipped), and rounds follow one another.  Block b
+// of the G blocks of a lane executes the items b, b+G, b+2G, ... in this order,
+// which keeps a rank's blocks on the same round and lets every op of a round
+// progress at the same rate.  Items only depend on items of earlier rounds, so
+// walking them in this order on co-resident blocks cannot deadlock.

@@ -15,9 +15,10 @@
 //   * simt: every thread moves 16-byte vectors with ld.relaxed.sys / st;
 //   * tma:  a producer thread streams tiles from peer memory into a shared
 //           memory ring with bulk async copies (cp.async.bulk + mbarrier
-//           complete_tx), consumer warps add in place, and bulk stores write
-//           the result to local and peer memory.  Few threads keep hundreds of
-//           KB in flight per block.
+//           complete_tx), consumer warps add in place, bulk stores write the
+//           result to local and peer memory, and a signal thread announces
+//           finished tiles, keeping the system-scope fence off the issue path.
+//           Few threads keep hundreds of KB in flight per block.
 //
 // Every wait (peer arrival, tile flag, pipeline barrier, exit) is bounded by a
 // %globaltimer deadline.  On expiry the block records a SarStatus, raises the
