@@ -48,6 +48,10 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--tiny", action="store_true", help="a 2-layer model for smoke tests")
     ap.add_argument("--lr", type=float, default=5e-5)
+    ap.add_argument("--grad-sync", default="ddp", choices=["ddp", "flat", "per-param"],
+                    help="ddp: DistributedDataParallel buckets overlapped with backward; flat: one all_reduce of "
+                         "the flattened gradients after backward (the reference's dp.py); per-param: one all_reduce "
+                         "per parameter (the reference's dp_llama.py)")
     ap.add_argument("--auto-straggler", action="store_true",
                     help="find the late rank at run time (StragglerMonitor) instead of trusting --straggler")
     args = ap.parse_args()
@@ -73,9 +77,18 @@ def main() -> int:
     torch.manual_seed(1234)   # the same initial weights everywhere; DDP broadcasts them anyway
     cfg = LlamaConfig.tiny() if args.tiny else LlamaConfig.llama32_1b()
     model = LlamaForCausalLM(cfg).to(dev, dtype=getattr(torch, args.dtype))
-    ddp = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
-    if args.backend == "stragglar":
-        ddp.register_comm_hook(None, sp.fused_avg_hook)
+    from stragglar_b200.parallel.grad_sync import FlatGradSync, allreduce_gradients_per_param
+    flat_sync = None
+    if args.grad_sync == "ddp":
+        ddp = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+        if args.backend == "stragglar":
+            ddp.register_comm_hook(None, sp.fused_avg_hook)
+    else:
+        ddp = model                       # gradients are averaged by hand after the backward pass
+        for p in model.parameters():
+            dist.broadcast(p.data, src=0)
+        if args.grad_sync == "flat":
+            flat_sync = FlatGradSync(model)
     opt = torch.optim.AdamW(ddp.parameters(), lr=args.lr)
     sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: min(1.0, (s + 1) / 50))
     gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
@@ -105,8 +118,12 @@ def main() -> int:
         torch.cuda.nvtx.range_pop()
         ev[1].record()
         torch.cuda.nvtx.range_push("Backward+AllReduce_Gradients")
-        loss.backward()                                    # the bucket AllReduces overlap this
+        loss.backward()                                    # with DDP the bucket AllReduces overlap this
         torch.cuda.nvtx.range_pop()
+        if args.grad_sync != "ddp":
+            torch.cuda.nvtx.range_push("AllReduce_Gradients")
+            flat_sync() if flat_sync is not None else allreduce_gradients_per_param(model)
+            torch.cuda.nvtx.range_pop()
         ev[2].record()
         opt.step(); sched.step(); opt.zero_grad(set_to_none=False)
         ev[3].record()

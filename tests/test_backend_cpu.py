@@ -189,3 +189,31 @@ def test_missing_rank_raises_after_the_timeout():
         run_ranks(2, _late_rank_times_out)
     finally:
         del os.environ["STRAGGLAR_TIMEOUT_MS"]
+
+
+def _grad_sync(rank, world):
+    from stragglar_b200.parallel.grad_sync import FlatGradSync, allreduce_gradients_per_param
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 3))
+    x = torch.randn(4, 8, generator=torch.Generator().manual_seed(10 + rank))
+    model(x).sum().backward()
+    mine = [p.grad.clone() for p in model.parameters()]
+    gathered = []
+    for g in mine:
+        parts = [torch.empty_like(g) for _ in range(world)]
+        dist.all_gather(parts, g)
+        gathered.append(torch.stack(parts).mean(0))
+    sync = FlatGradSync(model)           # flat buffer in the symmetric heap, 1/world fused
+    sync()
+    for p, want in zip(model.parameters(), gathered):
+        torch.testing.assert_close(p.grad, want, atol=1e-6, rtol=1e-5)
+    for p, g in zip(model.parameters(), mine):
+        p.grad.copy_(g)
+    nbytes = allreduce_gradients_per_param(model)
+    assert nbytes == sum(g.numel() * 4 for g in mine)
+    for p, want in zip(model.parameters(), gathered):
+        torch.testing.assert_close(p.grad, want, atol=1e-6, rtol=1e-5)
+
+
+def test_manual_gradient_sync_flat_and_per_parameter():
+    run_ranks(2, _grad_sync)

@@ -109,3 +109,13 @@ def test_env_report_runs_without_a_gpu():
     from stragglar_b200.utils import env_check
     info = env_check.report()
     assert "torch" in info and isinstance(info["gpus"], list)
+
+
+def test_detect_on_the_shipped_training_log():
+    import os
+    log = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "logs",
+                       "log_8_b200_llama1b_stragglar.txt")
+    with open(log) as f:
+        rep = detect.analyse(detect.parse_ar_times(f), skip_delay_steps=3)
+    assert rep.straggler == 7            # the rank that was held back 20 ms per step
+    assert 15.0 < rep.median_delay_ms < 25.0
