@@ -238,3 +238,55 @@ def host_allreduce(table, bufs: Sequence[np.ndarray], scale: float = 1.0, blocks
         return lib().sar_host_execute_program(table._h, ptrs, bufs[0].size, code, tile_elems, scale, blocks, dl,
                                               timeout_s)
     return lib().sar_host_execute(table._h, ptrs, bufs[0].size, code, tile_elems, scale, blocks, dl, timeout_s, repeats)
+
+
+_KIND_NAMES = {COPY: "copy", REDUCE: "reduce", REDUCE_PUSH: "match", PUSH: "push"}
+
+
+def describe(program: Program) -> str:
+    """Human-readable listing of a compiled program: per phase and rank, one
+    line per op (round, lane, kind, chunk and tile range, peers, versions)."""
+    out = []
+    for pi, t in enumerate(program.phases):
+        out.append(f"phase {pi}: channel {t.channel}, {t.num_chunks} chunks, {t.num_rounds} rounds, "
+                   f"participants {[r for r in range(t.n) if t.takes_part(r)]}, "
+                   f"link traffic {t.link_chunks():g} chunks per direction on the busiest rank"
+                   + (f", at most {t.blocks_hint} blocks per rank" if t.blocks_hint else ""))
+        for r in t.ranks:
+            if not len(r.ops):
+                continue
+            out.append(f"  rank {r.rank}: in {r.chunks_in:g} / out {r.chunks_out:g} chunks")
+            for o in r.ops:
+                kind, n = int(o["kind"]), int(o["nsrc"])
+                peers = [int(x) for x in o["src"][:n]]
+                vers = [int(x) for x in o["src_ver"][:n]]
+                part = "" if int(o["parts"]) == 1 else f" part {int(o['part']) + 1}/{int(o['parts'])}"
+                flags = ("+scale" if int(o["flags"]) & F_SCALE else "") + ("+own" if int(o["flags"]) & F_LOCAL else "")
+                arrow = "->" if kind == PUSH else "<-"
+                out.append(f"    round {int(o['round']):2d} lane {int(o['lane'])} {_KIND_NAMES[kind]:6s} chunk {int(o['chunk']):2d}{part} "
+                           f"{arrow} {peers} (needs v{vers}, own v{int(o['local_ver'])}) => own v{int(o['post_ver'])}"
+                           + (f", peer v{int(o['push_ver'])}" if kind in (PUSH, REDUCE_PUSH) else "") + (f" {flags}" if flags else ""))
+    return "\n".join(out)
+
+
+def main(argv=None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(description="compile a collective and list its per-rank op tables")
+    ap.add_argument("alg", choices=ALGORITHMS)
+    ap.add_argument("n", type=int)
+    ap.add_argument("--no-prephase", action="store_true", help="the pre-phase has already happened (DELAY = -1)")
+    ap.add_argument("--straggler", type=int, default=None, help="physical rank that plays logical rank n-1")
+    ap.add_argument("--schedule", default=None, help="file with a synthesizer printout to use instead of the built-in schedule")
+    args = ap.parse_args(argv)
+    sched = Schedule.parse(open(args.schedule).read()) if args.schedule else None
+    try:
+        prog = compile_program(args.alg, args.n, not args.no_prephase, args.straggler, sched)
+    except CompileError as e:
+        print(f"error: {e}")
+        return 1
+    print(describe(prog))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

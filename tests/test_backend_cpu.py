@@ -217,3 +217,42 @@ def _grad_sync(rank, world):
 
 def test_manual_gradient_sync_flat_and_per_parameter():
     run_ranks(2, _grad_sync)
+
+
+def _bigger_than_staging(rank, world):
+    # 1 MiB of staging (arena 2 MiB): 3 MiB tensors go through the arena in pieces
+    n = 786_432 + 5
+    x = _seeded(rank, n)
+    want = torch.stack([_seeded(r, n).double() for r in range(world)]).sum(0)
+    y = x.clone()
+    dist.all_reduce(y)
+    torch.testing.assert_close(y.double(), want, atol=1e-5, rtol=1e-6)
+    b = x.clone() if rank == 1 else torch.zeros(n)
+    dist.broadcast(b, src=1)
+    torch.testing.assert_close(b, _seeded(1, n))
+    out = torch.empty(world * n)
+    dist.all_gather_into_tensor(out, x)
+    for r in range(world):
+        torch.testing.assert_close(out[r * n:(r + 1) * n], _seeded(r, n))
+    rs = torch.empty(n)
+    dist.reduce_scatter_tensor(rs, torch.cat([_seeded(10 * q + rank, n) for q in range(world)]))
+    want_rs = torch.stack([_seeded(10 * rank + p, n).double() for p in range(world)]).sum(0)
+    torch.testing.assert_close(rs.double(), want_rs, atol=1e-5, rtol=1e-6)
+    r0 = x.clone()
+    dist.reduce(r0, dst=1)
+    if rank == 1:
+        torch.testing.assert_close(r0.double(), want, atol=1e-5, rtol=1e-6)
+    if rank == 0:
+        dist.send(x, dst=1)
+    elif rank == 1:
+        got = torch.empty(n)
+        dist.recv(got, src=0)
+        torch.testing.assert_close(got, _seeded(0, n))
+
+
+def test_tensors_larger_than_the_staging_area():
+    os.environ["STRAGGLAR_CPU_ARENA_MB"] = "2"
+    try:
+        run_ranks(2, _bigger_than_staging)
+    finally:
+        del os.environ["STRAGGLAR_CPU_ARENA_MB"]

@@ -209,3 +209,10 @@ def test_block_count_hints():
     assert sc.compile_table("ring", 8).blocks_hint == 0
     assert sc.compile_table("stragglar", 2).blocks_hint == 0 and sc.compile_table("stragglar", 1).blocks_hint == 0
     assert [t.blocks_hint for t in sc.compile_program("direct", 8).phases] == [0, 0]
+
+
+def test_table_listing_cli(capsys):
+    assert sc.main(["stragglar", "4", "--no-prephase"]) == 0
+    text = capsys.readouterr().out
+    assert "phase 0" in text and "match" in text and "rank 3" in text
+    assert sc.main(["rhd", "6"]) == 1 and "power-of-two" in capsys.readouterr().out
