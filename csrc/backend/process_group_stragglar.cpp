@@ -226,6 +226,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
     if (!(c.participants >> me & 1)) continue;
     int blocks = t.cuda() ? (opts_.blocks > 0 ? opts_.blocks : sar_cuda_pick_blocks(opts_.path, count * esize)) : 1;
     if (t.cuda() && opts_.blocks <= 0 && c.blocks_hint > 0 && c.blocks_hint < blocks) blocks = c.blocks_hint;
+    if (t.cuda() && opts_.blocks <= 0 && n == 1 && blocks == 128) blocks = 148;   // a lone rank: one block per SM
     const uint32_t tile_max = opts_.tile_bytes ? opts_.tile_bytes : (t.cuda() ? sar_cuda_default_tile_bytes(opts_.path) : (128u << 10));
     const uint32_t tile_elems = sar::pick_tile_elems(count, esize, (uint32_t)c.num_chunks, (uint32_t)blocks, 2048, tile_max);
     const SarGeom g = sar::make_geom(count, esize, (uint32_t)c.num_chunks, tile_elems);

@@ -159,6 +159,7 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
   const int path = o->path;
   int blocks = o->blocks > 0 ? o->blocks : sar_cuda_pick_blocks(path, count * esize);
   if (c->emulate && o->blocks <= 0) blocks = 4;   // all ranks share one device
+  if (n == 1 && o->blocks <= 0 && blocks == 128) blocks = 148;   // a lone rank streams its own memory: one block per SM
   const double timeout_s = o->timeout_s > 0 ? o->timeout_s : 10.0;
   const uint32_t tile_max = o->tile_bytes ? o->tile_bytes : sar_cuda_default_tile_bytes(path);
   std::vector<bool> delayed(n, false);
