@@ -115,3 +115,45 @@ def test_cli_module_runs():
                          cwd=os.path.dirname(os.path.dirname(__file__)))
     assert out.returncode == 0
     assert "Actual number of rounds 9" in out.stdout and "Optimal number of rounds 9.0" in out.stdout
+
+
+def test_rank_map_and_compact_form():
+    s = synthesize(8)
+    assert s.rank_map_for_straggler(2) == [0, 1, 7, 3, 4, 5, 6, 2]
+    assert s.rank_map_for_straggler(7) == list(range(8))
+    with pytest.raises(ScheduleError):
+        s.rank_map_for_straggler(8)
+    lines = s.compact().splitlines()
+    assert lines[0] == "R0: 0<->7 c0" and lines[1] == "R1: 1<->7 c1 | 0->3 c0" and len(lines) == 9
+
+
+def test_matchers_agree_on_cardinality_and_weight():
+    from stragglar_b200.synth.matching import _exact, _greedy, max_weight_matching
+    nodes = list(range(8))
+    edges = [(0, 1, 2), (1, 2, 1), (2, 3, 2), (3, 4, 1), (4, 5, 2), (5, 6, 1), (6, 7, 2), (0, 7, 1), (1, 6, 1)]
+    exact = _exact(nodes, edges)
+    assert len(exact) == 4 and sum(w for u, v, w in edges if (u, v) in exact or (v, u) in exact) == 8
+    nxm = max_weight_matching(nodes, edges)
+    assert len(nxm) == 4
+    g = _greedy(nodes, edges)
+    assert len(g) == 4 and len({x for p in g for x in p}) == 8
+
+
+def test_builtin_schedule_export_is_current():
+    import contextlib
+    from stragglar_b200.synth import export
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        export.main()
+    path = os.path.join(os.path.dirname(os.path.dirname(__file__)), "csrc", "core", "builtin_schedules.inc")
+    assert buf.getvalue() == open(path).read(), "run: python -m stragglar_b200.synth.export > csrc/core/builtin_schedules.inc"
+
+
+@pytest.mark.parametrize("script,args,needle", [("synthesizer_pow2.py", ["8"], "Actual number of rounds 9"),
+                                                ("synthesizer_nonpow2.py", ["6"], "Actual number of rounds 7"),
+                                                ("pad_buffers.py", ["8"], "1073744896"),
+                                                ("simulation.py", [], "Speedups for powers of two:")])
+def test_reference_named_scripts(script, args, needle):
+    root = os.path.dirname(os.path.dirname(__file__))
+    out = subprocess.run([sys.executable, os.path.join(root, "stragglar", script), *args], capture_output=True, text=True)
+    assert out.returncode == 0 and needle in out.stdout
