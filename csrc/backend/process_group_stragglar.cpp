@@ -105,6 +105,17 @@ const sar::Program& ProcessGroupStragglar::program() {
   try {
     return programs_.emplace(key, sar::build_program(alg, getSize(), true, opts_.straggler, sp)).first->second;
   } catch (const std::exception& e) {
+    // StragglAR schedules exist for even rank counts (and halving-doubling for powers of two);
+    // a group of another size, e.g. a sub-group of three ranks, is served by the ring instead
+    if (alg != "ring" && opts_.schedule_text.empty()) {
+      try {
+        auto& p = programs_.emplace(key, sar::build_program("ring", getSize(), true, opts_.straggler, nullptr)).first->second;
+        TORCH_WARN_ONCE("stragglar backend: '", alg, "' is not available for ", getSize(), " ranks (", e.what(),
+                        "); using ring for this group");
+        return p;
+      } catch (const std::exception&) {
+      }
+    }
     TORCH_CHECK(false, "stragglar backend: cannot build '", alg, "' for ", getSize(), " ranks: ", e.what());
   }
 }
@@ -532,6 +543,24 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::reduce_scatter(std::vector
   }
   auto w = _reduce_scatter_base(outputs[0], flat, opts);
   if (flat.is_cuda()) c10::cuda::CUDACachingAllocator::recordStream(flat.storage().data_ptr(), *cuda_.stream);
+  return w;
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::reduce_scatter_tensor_coalesced(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs, const c10d::ReduceScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == inputs.size() && !inputs.empty(), "size mismatch");
+  c10::intrusive_ptr<c10d::Work> w;
+  for (size_t i = 0; i < inputs.size(); ++i) w = _reduce_scatter_base(outputs[i], inputs[i], opts);
+  return w;   // the operations run in order on the communication stream: the last one's completion covers all
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allgather_coalesced(std::vector<std::vector<at::Tensor>>& output_lists, std::vector<at::Tensor>& inputs, const c10d::AllgatherOptions& opts) {
+  TORCH_CHECK(output_lists.size() == inputs.size() && !inputs.empty(), "size mismatch");
+  c10::intrusive_ptr<c10d::Work> w;
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    std::vector<std::vector<at::Tensor>> outs{output_lists[i]};
+    std::vector<at::Tensor> in{inputs[i]};
+    w = allgather(outs, in, opts);
+  }
   return w;
 }
 

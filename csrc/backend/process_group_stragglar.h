@@ -97,6 +97,12 @@ class ProcessGroupStragglar : public c10d::Backend {
                                                 const c10d::ReduceScatterOptions& opts) override;
   c10::intrusive_ptr<c10d::Work> _reduce_scatter_base(at::Tensor& output, at::Tensor& input,
                                                       const c10d::ReduceScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> reduce_scatter_tensor_coalesced(std::vector<at::Tensor>& outputs,
+                                                                 std::vector<at::Tensor>& inputs,
+                                                                 const c10d::ReduceScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> allgather_coalesced(std::vector<std::vector<at::Tensor>>& output_lists,
+                                                     std::vector<at::Tensor>& inputs,
+                                                     const c10d::AllgatherOptions& opts) override;
   c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& output, at::Tensor& input, std::vector<int64_t>& out_splits,
                                                std::vector<int64_t>& in_splits, const c10d::AllToAllOptions& opts) override;
   c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,

@@ -134,6 +134,16 @@ def _collectives(rank, world):
         torch.testing.assert_close(h.double(), wanth, atol=tol, rtol=2e-2)
     with pytest.raises(RuntimeError):
         dist.all_reduce(torch.ones(4), op=dist.ReduceOp.MAX)
+    # coalesced forms, reached through the functional collectives (what FSDP-style code uses)
+    import torch.distributed._functional_collectives as fc
+    ins = [torch.arange(world * 3).float() + rank, torch.arange(world * 5).float() * 2 + rank]
+    outs = [fc.wait_tensor(t) for t in fc.reduce_scatter_tensor_coalesced(ins, "sum", [0, 0], dist.group.WORLD)]
+    torch.testing.assert_close(outs[0], world * (torch.arange(3).float() + 3 * rank) + sum(range(world)))
+    torch.testing.assert_close(outs[1], world * 2 * (torch.arange(5).float() + 5 * rank) + sum(range(world)))
+    gouts = [fc.wait_tensor(t) for t in fc.all_gather_into_tensor_coalesced(
+        [torch.full((2,), float(rank)), torch.full((4,), float(rank + 10))], dist.group.WORLD)]
+    assert torch.equal(gouts[0], torch.arange(world).repeat_interleave(2).float())
+    assert torch.equal(gouts[1], (torch.arange(world) + 10).repeat_interleave(4).float())
 
 
 @pytest.mark.parametrize("world", [2, 4])
@@ -256,3 +266,27 @@ def test_tensors_larger_than_the_staging_area():
         run_ranks(2, _bigger_than_staging)
     finally:
         del os.environ["STRAGGLAR_CPU_ARENA_MB"]
+
+
+def _subgroups(rank, world):
+    # a group of three ranks has no StragglAR schedule: it is served by the ring
+    g3 = dist.new_group([0, 1, 2], backend="stragglar")
+    g2 = dist.new_group([1, 3], backend="stragglar")
+    x = torch.full((1001,), float(rank + 1))
+    if rank in (0, 1, 2):
+        dist.all_reduce(x, group=g3)
+        assert (x == 6).all()
+    y = torch.full((77,), float(rank + 1))
+    if rank in (1, 3):
+        dist.all_reduce(y, group=g2)
+        assert (y == 6).all()
+        out = [torch.empty(3) for _ in range(2)]
+        dist.all_gather(out, torch.full((3,), float(rank)), group=g2)
+        assert out[0][0] == 1 and out[1][0] == 3
+    z = torch.ones(10)
+    dist.all_reduce(z)
+    assert (z == world).all()
+
+
+def test_subgroups_and_odd_sizes():
+    run_ranks(4, _subgroups)
