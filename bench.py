@@ -137,7 +137,7 @@ def run_reference(args) -> int:
         print(json.dumps(out), flush=True)
     finally:
         open(done, "w").close()
-        time.sleep(1.0)
+        time.sleep(3.0)    # the waiting ranks poll twice a second
         try:
             os.remove(done)
         except OSError:
