@@ -1,0 +1,72 @@
+// Race check of the table protocol under ThreadSanitizer.
+//
+// Builds every algorithm for several rank counts (all lowerings), runs it with
+// the host executor -- several threads per rank, the same item order, flags,
+// arrival and exit words as the CUDA kernels -- and checks the sums.  Compiled
+// with -fsanitize=thread, every unordered pair of accesses to a buffer element
+// (a read of a slot that may still be overwritten, a write that is not ordered
+// after the reads of the value it destroys) is reported as a data race: this
+// is the dynamic counterpart of the compiler's static hazard check, and stands
+// in for compute-sanitizer's racecheck, which is not available for the GPU runs.
+//
+//   g++ -std=c++17 -O1 -g -fsanitize=thread -pthread host_exec_race_check.cpp ../plan.cpp ../host_exec.cpp -o race_check && ./race_check
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <string>
+#include <vector>
+
+#include "../host_exec.h"
+#include "../plan.h"
+
+static float uniform(uint64_t seed, uint64_t i) {
+  uint64_t x = (i + 1) * 0x9E3779B97F4A7C15ull + seed * 0xD1B54A32D192ED03ull;
+  x ^= x >> 32; x *= 0xD6E8FEB86659FD93ull; x ^= x >> 32;
+  return (float)(uint32_t)(x >> 40) * (2.0f / 16777216.0f) - 1.0f;
+}
+
+int main() {
+  int failures = 0, runs = 0;
+  const char* algs[] = {"stragglar", "stragglar_a2a", "ring", "rhd", "direct", "rsag"};
+  for (const char* copy : {"pull", "push"})
+    for (const char* lanes : {"1", "2"}) {
+      setenv("STRAGGLAR_COPY", copy, 1);
+      setenv("STRAGGLAR_LANES", lanes, 1);
+      for (const char* alg : algs)
+        for (int n : {2, 4, 6, 8})
+          for (int straggler : {-1, 1}) {
+            if (std::string(alg) == "rhd" && (n & (n - 1))) continue;
+            if (straggler >= n) continue;
+            sar::Program prog;
+            try {
+              prog = sar::build_program(alg, n, true, straggler, nullptr);
+            } catch (const std::exception& e) {
+              printf("compile failed: %s n=%d: %s\n", alg, n, e.what());
+              ++failures;
+              continue;
+            }
+            const uint64_t count = 997 * n + 3;
+            std::vector<std::vector<float>> buf(n, std::vector<float>(count));
+            std::vector<double> want(count, 0.0);
+            for (int r = 0; r < n; ++r)
+              for (uint64_t i = 0; i < count; ++i) { buf[r][i] = uniform(r, i); want[i] += buf[r][i]; }
+            std::vector<void*> ptrs(n);
+            for (int r = 0; r < n; ++r) ptrs[r] = buf[r].data();
+            std::vector<double> delay(n, 0.0);
+            delay[straggler < 0 ? n - 1 : straggler] = 2.0;   // the straggler is 2 ms late
+            const uint32_t st = sar::host_execute_program(prog, ptrs.data(), count, SAR_F32, 32, 0.5f, 4, delay.data(), 20.0);
+            ++runs;
+            if (st) { printf("status %u: %s n=%d copy=%s lanes=%s\n", st, alg, n, copy, lanes); ++failures; continue; }
+            for (int r = 0; r < n; ++r)
+              for (uint64_t i = 0; i < count; ++i)
+                if (std::fabs(buf[r][i] - 0.5 * want[i]) > 1e-5) {
+                  printf("wrong value: %s n=%d copy=%s lanes=%s rank %d elem %llu\n", alg, n, copy, lanes, r, (unsigned long long)i);
+                  ++failures;
+                  r = n;
+                  break;
+                }
+          }
+    }
+  printf("%d runs, %d failures\n", runs, failures);
+  return failures ? 1 : 0;
+}
