@@ -164,25 +164,11 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
   const uint32_t tile_max = o->tile_bytes ? o->tile_bytes : sar_cuda_default_tile_bytes(path);
   std::vector<bool> delayed(n, false);
 
-  if (o->timed) {
-    // device-side start barrier on the last channel, then the start event
-    const uint32_t ep = ++c->epoch[SAR_NUM_CHANNELS - 1];
-    if (!c->emulate) {
-      SarCtrl* ctrl[SAR_MAX_RANKS];
-      for (int r = 0; r < n; ++r) ctrl[r] = c->ranks[r].ctrl + (SAR_NUM_CHANNELS - 1);
-      for (int r = 0; r < n; ++r) {
-        CK(cudaSetDevice(c->ranks[r].dev));
-        CK((cudaError_t)sar_cuda_barrier(ctrl, r, n, (1u << n) - 1u, ep, (uint64_t)(timeout_s * 1e9), c->ranks[r].status, c->ranks[r].stream));
-      }
-    }
-    for (int r = 0; r < n; ++r) {
-      if (c->emulate && r > 0) break;
-      CK(cudaSetDevice(c->ranks[r].dev));
-      CK(cudaEventRecord(c->ranks[r].ev0, c->ranks[r].stream));
-    }
-  }
   for (int r = 0; r < n; ++r) c->ranks[r].timed = o->timed != 0;
 
+  // ---- prepare every phase: geometry, device tables (uploaded on first use), launch parameters
+  struct PhaseLaunch { std::vector<SarLaunchParams> hp; int blocks; uint32_t parts; };
+  std::vector<PhaseLaunch> launches(nph);
   for (int ph = 0; ph < nph; ++ph) {
     const sar_table* t = sar_program_phase(prog, ph);
     const int ch = sar_table_channel(t);
@@ -198,10 +184,11 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       if (err) snprintf(err, errlen, "buffer too large for the flag array");
       return 1;
     }
-    std::vector<SarLaunchParams> hp(n);
+    PhaseLaunch& L = launches[ph];
+    L.hp.resize(n); L.blocks = pblocks; L.parts = parts;
     for (int r = 0; r < n; ++r) {
       Rank& rk = c->ranks[r];
-      SarLaunchParams& P = hp[r];
+      SarLaunchParams& P = L.hp[r];
       memset(&P, 0, sizeof(P));
       for (int q = 0; q < n; ++q) {
         P.comm.flags[q] = c->ranks[q].flags + (size_t)ch * SAR_FLAG_CAPACITY;
@@ -219,31 +206,50 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       P.delay_ns = 0;
       if (c->emulate && delay_ns && delay_ns[r] && !delayed[r] && (parts >> r & 1)) { P.delay_ns = delay_ns[r]; delayed[r] = true; }
     }
-    if (c->emulate) {
-      CK(cudaSetDevice(c->ranks[0].dev));
-      CK(cudaMemcpyAsync(c->d_params, hp.data(), sizeof(SarLaunchParams) * n, cudaMemcpyHostToDevice, c->ranks[0].stream));
+  }
+
+  if (c->emulate) {
+    // every rank on one device: one cooperative launch per phase on one stream
+    Rank& r0 = c->ranks[0];
+    CK(cudaSetDevice(r0.dev));
+    if (o->timed) CK(cudaEventRecord(r0.ev0, r0.stream));
+    for (int ph = 0; ph < nph; ++ph) {
+      CK(cudaMemcpyAsync(c->d_params, launches[ph].hp.data(), sizeof(SarLaunchParams) * n, cudaMemcpyHostToDevice, r0.stream));
       // the copy is from pageable memory: it has completed with respect to the host buffer on return
-      cudaError_t e = (cudaError_t)sar_cuda_launch_emulated(c->d_params, n, dtype, path, pblocks, o->threads, c->ranks[0].stream);
+      cudaError_t e = (cudaError_t)sar_cuda_launch_emulated(c->d_params, n, dtype, path, launches[ph].blocks, o->threads, r0.stream);
       if (e != cudaSuccess) {
-        if (err) snprintf(err, errlen, "emulated launch (%d ranks x %d blocks): %s", n, pblocks, cudaGetErrorString(e));
+        if (err) snprintf(err, errlen, "emulated launch (%d ranks x %d blocks): %s", n, launches[ph].blocks, cudaGetErrorString(e));
         return (int)e;
       }
-    } else {
-      for (int r = 0; r < n; ++r) {
-        if (!(parts >> r & 1)) continue;
-        Rank& rk = c->ranks[r];
-        CK(cudaSetDevice(rk.dev));
-        if (delay_ns && delay_ns[r] && !delayed[r]) { CK((cudaError_t)sar_cuda_delay(delay_ns[r], rk.stream)); delayed[r] = true; }
-        CK((cudaError_t)sar_cuda_launch(&hp[r], path, pblocks, o->threads, rk.stream));
-      }
     }
+    if (o->timed) CK(cudaEventRecord(r0.ev1, r0.stream));
+    return 0;
   }
+
+  // ---- one rank per device.  Everything of a rank is enqueued before the next rank is touched:
+  // [start barrier, start event,] [delay,] its phases [, stop event].  The start barrier holds
+  // every stream until the last rank's barrier kernel runs, by which time the work of all
+  // other ranks is already queued behind theirs, so the host's launch order stays out of the
+  // timed window.
+  uint32_t barrier_epoch = 0;
+  SarCtrl* bctrl[SAR_MAX_RANKS] = {};
   if (o->timed) {
-    for (int r = 0; r < n; ++r) {
-      if (c->emulate && r > 0) break;
-      CK(cudaSetDevice(c->ranks[r].dev));
-      CK(cudaEventRecord(c->ranks[r].ev1, c->ranks[r].stream));
+    barrier_epoch = ++c->epoch[SAR_NUM_CHANNELS - 1];
+    for (int r = 0; r < n; ++r) bctrl[r] = c->ranks[r].ctrl + (SAR_NUM_CHANNELS - 1);
+  }
+  for (int r = 0; r < n; ++r) {
+    Rank& rk = c->ranks[r];
+    CK(cudaSetDevice(rk.dev));
+    if (o->timed) {
+      CK((cudaError_t)sar_cuda_barrier(bctrl, r, n, (1u << n) - 1u, barrier_epoch, (uint64_t)(timeout_s * 1e9), rk.status, rk.stream));
+      CK(cudaEventRecord(rk.ev0, rk.stream));
     }
+    for (int ph = 0; ph < nph; ++ph) {
+      if (!(launches[ph].parts >> r & 1)) continue;
+      if (delay_ns && delay_ns[r] && !delayed[r]) { CK((cudaError_t)sar_cuda_delay(delay_ns[r], rk.stream)); delayed[r] = true; }
+      CK((cudaError_t)sar_cuda_launch(&launches[ph].hp[r], path, launches[ph].blocks, o->threads, rk.stream));
+    }
+    if (o->timed) CK(cudaEventRecord(rk.ev1, rk.stream));
   }
   return 0;
 }
