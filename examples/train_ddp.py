@@ -15,6 +15,12 @@ rank ``--straggler`` is held back ``--delay-ms`` on the device at the start
 of every step, and the schedule is re-labelled so that it plays the last rank.
 ``--backend nccl`` runs the same loop on stock NCCL for comparison.
 
+``--model-dir DIR`` loads a checkpoint in the Hugging Face layout (written by ``examples/load_model.py`` or by
+``save_pretrained``) instead of initialising at random; ``--data-dir DIR`` trains on the instruction dataset
+prepared by ``examples/load_dataset.py`` (prompt format, 512-token padding, batch 4 and ``DistributedSampler`` as
+in dp.py:87-119) instead of uniform random token ids; ``--cpu`` runs the whole loop on CPU tensors (the backend's
+host executor, or gloo), which is how the script is tested without a GPU.
+
 Per step and rank it prints the reference's log line
 (``Rank r | Step s | Forward Time ... | AR Time ...``, dp.py:283), which
 ``python -m stragglar_b200.detect`` reads; rank 0 also prints tokens/s.
@@ -54,6 +60,11 @@ def main() -> int:
                          "per parameter (the reference's dp_llama.py)")
     ap.add_argument("--auto-straggler", action="store_true",
                     help="find the late rank at run time (StragglerMonitor) instead of trusting --straggler")
+    ap.add_argument("--model-dir", default=None, help="checkpoint directory (config.json + safetensors)")
+    ap.add_argument("--data-dir", default=None, help="dataset directory written by examples/load_dataset.py")
+    ap.add_argument("--samples", type=int, default=8192, help="records of --data-dir to use")
+    ap.add_argument("--max-length", type=int, default=512, help="tokens per example with --data-dir")
+    ap.add_argument("--cpu", action="store_true", help="CPU tensors (backend stragglar or gloo); for tests")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -61,26 +72,59 @@ def main() -> int:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29500")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+    cuda = not args.cpu
+    if cuda:
+        torch.cuda.set_device(local)
+    dev = torch.device("cuda", local) if cuda else torch.device("cpu")
     straggler = args.straggler if args.straggler >= 0 else world - 1
 
     if args.backend == "stragglar":
         import stragglar_b200.parallel as sp
-        from stragglar_b200 import ops
         sp.configure(alg=args.alg, straggler=straggler)
         dist.init_process_group("stragglar", rank=rank, world_size=world)
-    else:
-        from stragglar_b200 import ops
+    elif cuda:
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    if cuda:
+        from stragglar_b200 import ops
+
+    class Stamp:
+        """A point in time on the device stream (CUDA event) or on the host (--cpu)."""
+        def __init__(self):
+            self.ev = torch.cuda.Event(enable_timing=True) if cuda else None
+            self.t = 0.0
+        def record(self):
+            if cuda:
+                self.ev.record()
+            else:
+                self.t = time.perf_counter()
+        def ms_until(self, other):
+            return self.ev.elapsed_time(other.ev) if cuda else (other.t - self.t) * 1e3
+
+    def sync():
+        if cuda:
+            torch.cuda.synchronize()
+
+    def nvtx_push(name):
+        if cuda:
+            torch.cuda.nvtx.range_push(name)
+
+    def nvtx_pop():
+        if cuda:
+            torch.cuda.nvtx.range_pop()
 
     torch.manual_seed(1234)   # the same initial weights everywhere; DDP broadcasts them anyway
-    cfg = LlamaConfig.tiny() if args.tiny else LlamaConfig.llama32_1b()
-    model = LlamaForCausalLM(cfg).to(dev, dtype=getattr(torch, args.dtype))
+    if args.model_dir:
+        model = LlamaForCausalLM.from_pretrained(args.model_dir).to(dev, dtype=getattr(torch, args.dtype))
+        cfg = model.cfg
+    else:
+        cfg = LlamaConfig.tiny() if args.tiny else LlamaConfig.llama32_1b()
+        model = LlamaForCausalLM(cfg).to(dev, dtype=getattr(torch, args.dtype))
     from stragglar_b200.parallel.grad_sync import FlatGradSync, allreduce_gradients_per_param
     flat_sync = None
     if args.grad_sync == "ddp":
-        ddp = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+        ddp = DDP(model, device_ids=[local] if cuda else None, bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
         if args.backend == "stragglar":
             ddp.register_comm_hook(None, sp.fused_avg_hook)
     else:
@@ -92,6 +136,26 @@ def main() -> int:
     opt = torch.optim.AdamW(ddp.parameters(), lr=args.lr)
     sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: min(1.0, (s + 1) / 50))
     gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    batches = None
+    seq_len = args.seq_len
+    if args.data_dir:
+        from torch.utils.data import DataLoader
+        from torch.utils.data.distributed import DistributedSampler
+        from stragglar_b200.utils.data import InstructionDataset, load_records, load_tokenizer
+        tok = load_tokenizer(args.model_dir)
+        assert tok.vocab_size <= cfg.vocab_size, f"tokenizer has {tok.vocab_size} tokens, the model {cfg.vocab_size}"
+        ds = InstructionDataset(load_records(args.data_dir, args.samples), tok, args.max_length)
+        sampler = DistributedSampler(ds, num_replicas=world, rank=rank, shuffle=True, seed=0)
+        loader = DataLoader(ds, batch_size=args.micro_batch, sampler=sampler, drop_last=True, pin_memory=cuda)
+        seq_len = args.max_length
+
+        def batch_stream():
+            epoch = 0
+            while True:
+                sampler.set_epoch(epoch)
+                yield from loader
+                epoch += 1
+        batches = batch_stream()
     nparams = sum(p.numel() for p in model.parameters())
     grad_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
     if rank == 0:
@@ -101,36 +165,46 @@ def main() -> int:
     monitor = None
     if args.backend == "stragglar" and args.auto_straggler:
         monitor = sp.StragglerMonitor(window=5, threshold=0.8, device=dev)
-    tokens_per_step = world * args.micro_batch * args.seq_len
+    tokens_per_step = world * args.micro_batch * seq_len
     times = []
     for step in range(args.warmup + args.steps):
-        ids_host = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq_len), generator=gen).pin_memory()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        if batches is not None:
+            batch = next(batches)
+            ids_host, labels_host = batch["input_ids"], batch["labels"]
+        else:
+            ids_host = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq_len), generator=gen)
+            labels_host = ids_host
+        if cuda:
+            ids_host, labels_host = ids_host.pin_memory(), labels_host.pin_memory()
+        ev = [Stamp() for _ in range(4)]
         dist.barrier()
-        torch.cuda.synchronize()
-        t_host = time.perf_counter()
+        sync()
         ev[0].record()
         if rank == straggler and args.delay_ms > 0 and world > 1:
-            ops.delay(args.delay_ms)                       # the persistent straggler
+            if cuda:
+                ops.delay(args.delay_ms)                   # the persistent straggler, held back on the device
+            else:
+                time.sleep(args.delay_ms / 1e3)
         ids = ids_host.to(dev, non_blocking=True)
-        torch.cuda.nvtx.range_push("Forward")
-        loss = ddp(ids, labels=ids)
-        torch.cuda.nvtx.range_pop()
+        labels = ids if labels_host is ids_host else labels_host.to(dev, non_blocking=True)
+        nvtx_push("Forward")
+        loss = ddp(ids, labels=labels)
+        nvtx_pop()
         ev[1].record()
-        torch.cuda.nvtx.range_push("Backward+AllReduce_Gradients")
+        nvtx_push("Backward+AllReduce_Gradients")
         loss.backward()                                    # with DDP the bucket AllReduces overlap this
-        torch.cuda.nvtx.range_pop()
+        nvtx_pop()
         if args.grad_sync != "ddp":
-            torch.cuda.nvtx.range_push("AllReduce_Gradients")
+            nvtx_push("AllReduce_Gradients")
             flat_sync() if flat_sync is not None else allreduce_gradients_per_param(model)
-            torch.cuda.nvtx.range_pop()
+            nvtx_pop()
         ev[2].record()
         opt.step(); sched.step(); opt.zero_grad(set_to_none=False)
         ev[3].record()
         loss_val = loss.item()                             # device -> host read of the step's result
-        torch.cuda.synchronize()
-        iter_ms = ev[0].elapsed_time(ev[3])
-        fwd, bwd = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
+        sync()
+        iter_ms = ev[0].ms_until(ev[3])
+        fwd, bwd = ev[0].ms_until(ev[1]), ev[1].ms_until(ev[2])
         # the gradient AllReduces overlap the backward pass, so "AR Time" is the backward time
         print(format_step(rank, step, fwd, bwd, loss_val, iter_ms, bwd, grad_bytes) + "\n", flush=True)
         t = torch.tensor([iter_ms], device=dev)

@@ -12,9 +12,11 @@ AllReduce, not the model.
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 from dataclasses import dataclass
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 import torch.nn as nn
@@ -33,10 +35,39 @@ class LlamaConfig:
     rms_eps: float = 1e-5
     tie_embeddings: bool = True
     max_seq_len: int = 8192
+    # Llama-3 frequency scaling of the rotary embedding ({"factor", "low_freq_factor", "high_freq_factor",
+    # "original_max_position_embeddings"}); None = plain rotary embedding
+    rope_scaling: Optional[dict] = None
 
     @classmethod
     def llama32_1b(cls) -> "LlamaConfig":
-        return cls()
+        """The shape (and rotary scaling) of the Llama-3.2-1B checkpoint."""
+        return cls(max_seq_len=131072, rope_scaling={"factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                                      "original_max_position_embeddings": 8192})
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "LlamaConfig":
+        """From the ``config.json`` of a Hugging Face Llama checkpoint."""
+        rs = d.get("rope_scaling")
+        if rs is not None and rs.get("rope_type", rs.get("type")) not in ("llama3",):
+            rs = None
+        return cls(vocab_size=d["vocab_size"], hidden_size=d["hidden_size"], intermediate_size=d["intermediate_size"],
+                   num_layers=d["num_hidden_layers"], num_heads=d["num_attention_heads"],
+                   num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
+                   rope_theta=float(d.get("rope_theta", 10000.0)), rms_eps=float(d.get("rms_norm_eps", 1e-5)),
+                   tie_embeddings=bool(d.get("tie_word_embeddings", False)),
+                   max_seq_len=int(d.get("max_position_embeddings", 8192)), rope_scaling=rs)
+
+    def to_hf(self) -> dict:
+        d = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": self.vocab_size,
+             "hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size,
+             "num_hidden_layers": self.num_layers, "num_attention_heads": self.num_heads,
+             "num_key_value_heads": self.num_kv_heads, "head_dim": self.head_dim, "hidden_act": "silu",
+             "rope_theta": self.rope_theta, "rms_norm_eps": self.rms_eps, "tie_word_embeddings": self.tie_embeddings,
+             "max_position_embeddings": self.max_seq_len, "attention_bias": False, "mlp_bias": False}
+        if self.rope_scaling is not None:
+            d["rope_scaling"] = dict(self.rope_scaling, rope_type="llama3")
+        return d
 
     @classmethod
     def tiny(cls) -> "LlamaConfig":
@@ -67,8 +98,15 @@ class RMSNorm(nn.Module):
         return (x.to(dtype)) * self.weight
 
 
-def rope_tables(seq_len: int, head_dim: int, theta: float, device, dtype=torch.float32):
+def rope_tables(seq_len: int, head_dim: int, theta: float, device, dtype=torch.float32, scaling: Optional[dict] = None):
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    if scaling is not None:
+        # Llama-3 scaling: long wavelengths are stretched by `factor`, short ones kept, the band between blended
+        factor, lo, hi = float(scaling["factor"]), float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        orig = float(scaling["original_max_position_embeddings"])
+        wavelen = 2.0 * math.pi / inv
+        smooth = ((orig / wavelen - lo) / (hi - lo)).clamp(0.0, 1.0)
+        inv = (1.0 - smooth) * inv / factor + smooth * inv
     t = torch.arange(seq_len, device=device, dtype=torch.float32)
     freqs = torch.outer(t, inv)
     return freqs.cos().to(dtype), freqs.sin().to(dtype)
@@ -142,12 +180,14 @@ class LlamaForCausalLM(nn.Module):
         if isinstance(m, (nn.Linear, nn.Embedding)):
             nn.init.normal_(m.weight, mean=0.0, std=0.02)
 
-    def forward(self, input_ids, labels: Optional[torch.Tensor] = None):
+    def forward(self, input_ids, labels: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None):
         """Returns the logits, or the mean next-token cross-entropy when
-        ``labels`` is given (shifted inside, as Hugging Face models do)."""
+        ``labels`` is given (shifted inside, as Hugging Face models do; label -100 is ignored).
+        ``attention_mask`` is accepted for batches that carry one and not needed: attention is causal and the
+        padding sits on the right, so no real token attends to padding, and padded positions have label -100."""
         B, S = input_ids.shape
         x = self.embed_tokens(input_ids)
-        cos, sin = rope_tables(S, self.cfg.head_dim, self.cfg.rope_theta, x.device, x.dtype)
+        cos, sin = rope_tables(S, self.cfg.head_dim, self.cfg.rope_theta, x.device, x.dtype, self.cfg.rope_scaling)
         for layer in self.layers:
             x = layer(x, cos, sin)
         x = self.norm(x)
@@ -156,3 +196,52 @@ class LlamaForCausalLM(nn.Module):
             return F.linear(x, w)
         logits = F.linear(x[:, :-1], w)
         return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), labels[:, 1:].reshape(-1))
+
+    # ---- Hugging Face checkpoint layout (config.json + model.safetensors), so that a directory written by
+    # ``AutoModelForCausalLM.save_pretrained`` (motivation/load_model.py) can be loaded and vice versa
+    def hf_state_dict(self) -> Dict[str, torch.Tensor]:
+        out = {}
+        for k, v in self.state_dict().items():
+            out[k if k.startswith("lm_head.") else "model." + k] = v.detach().contiguous()
+        return out
+
+    def load_hf_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        own = {}
+        for k, v in sd.items():
+            if k == "lm_head.weight":
+                if self.lm_head is not None:
+                    own[k] = v
+                continue               # tied: the head is the embedding
+            own[k[len("model."):] if k.startswith("model.") else k] = v
+        missing, unexpected = self.load_state_dict(own, strict=False)
+        missing = [m for m in missing if not (m == "lm_head.weight" and "embed_tokens.weight" in own)]
+        if "lm_head.weight" in self.state_dict() and "lm_head.weight" not in own:
+            self.lm_head.weight.data.copy_(self.embed_tokens.weight.data)   # checkpoint with tied weights
+        if missing or unexpected:
+            raise KeyError(f"checkpoint does not match the model: missing {missing}, unexpected {list(unexpected)}")
+
+    def save_pretrained(self, directory: str) -> None:
+        from safetensors.torch import save_file
+        os.makedirs(directory, exist_ok=True)
+        with open(os.path.join(directory, "config.json"), "w") as f:
+            json.dump(dict(self.cfg.to_hf(), torch_dtype=str(next(self.parameters()).dtype).replace("torch.", "")), f, indent=1)
+        save_file(self.hf_state_dict(), os.path.join(directory, "model.safetensors"), metadata={"format": "pt"})
+
+    @classmethod
+    def from_pretrained(cls, directory: str, dtype: Optional[torch.dtype] = None) -> "LlamaForCausalLM":
+        """Loads ``config.json`` and the weights (``*.safetensors``, sharded or not, else ``pytorch_model.bin``)."""
+        with open(os.path.join(directory, "config.json")) as f:
+            cfg = LlamaConfig.from_hf(json.load(f))
+        with torch.device("meta"):
+            model = cls(cfg)
+        model = model.to_empty(device="cpu")
+        sd: Dict[str, torch.Tensor] = {}
+        shards = sorted(fn for fn in os.listdir(directory) if fn.endswith(".safetensors"))
+        if shards:
+            from safetensors.torch import load_file
+            for fn in shards:
+                sd.update(load_file(os.path.join(directory, fn)))
+        else:
+            sd = torch.load(os.path.join(directory, "pytorch_model.bin"), map_location="cpu", weights_only=True)
+        model.load_hf_state_dict(sd)
+        return model.to(dtype) if dtype is not None else model
