@@ -125,6 +125,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="find the persistent straggler in a training log")
     ap.add_argument("log")
     ap.add_argument("--skip", type=int, default=1, help="steps left out of the delay statistics")
+    ap.add_argument("--cdf", metavar="FILE", help="write the empirical CDF of the straggler delay (delay_ms,fraction) "
+                                                  "as CSV; FILE.png is drawn too when matplotlib is installed")
     args = ap.parse_args(argv)
     with open(args.log) as f:
         rep = analyse(parse_ar_times(f), args.skip)
@@ -133,6 +135,22 @@ def main(argv=None) -> int:
         print(f"Rank {r}    {pct:.1f}")
     print(f"straggler: rank {rep.straggler}; delay mean {rep.mean_delay_ms:.1f} ms, "
           f"median {rep.median_delay_ms:.1f} ms, max {rep.max_delay_ms:.1f} ms over {len(rep.delays_ms)} steps")
+    if args.cdf:
+        pts = rep.cdf()
+        with open(args.cdf, "w") as f:
+            f.write("delay_ms,fraction\n")
+            for x, y in pts:
+                f.write(f"{x:.4f},{y:.6f}\n")
+        try:   # the plot of the reference's notebook (motivation/log_proc.ipynb, last cell)
+            import matplotlib
+            matplotlib.use("Agg")
+            import matplotlib.pyplot as plt
+            plt.figure(figsize=(5, 3.2))
+            plt.step([p[0] for p in pts], [p[1] for p in pts], where="post")
+            plt.xlabel("straggler delay (ms)"); plt.ylabel("CDF"); plt.grid(alpha=0.3); plt.tight_layout()
+            plt.savefig(args.cdf + ".png", dpi=150)
+        except ImportError:
+            pass
     return 0
 
 

@@ -119,3 +119,15 @@ def test_detect_on_the_shipped_training_log():
         rep = detect.analyse(detect.parse_ar_times(f), skip_delay_steps=3)
     assert rep.straggler == 7            # the rank that was held back 20 ms per step
     assert 15.0 < rep.median_delay_ms < 25.0
+
+
+def test_detect_cli_writes_the_delay_cdf(tmp_path, capsys):
+    log = tmp_path / "train.log"
+    log.write_text(LOG)
+    out = tmp_path / "cdf.csv"
+    assert detect.main([str(log), "--cdf", str(out), "--skip", "0"]) == 0
+    assert "straggler: rank 2" in capsys.readouterr().out
+    rows = out.read_text().strip().splitlines()
+    assert rows[0] == "delay_ms,fraction"
+    pts = [tuple(map(float, r.split(","))) for r in rows[1:]]
+    assert pts == sorted(pts) and pts[-1][1] == 1.0 and len(pts) == 3
