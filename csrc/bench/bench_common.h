@@ -46,6 +46,7 @@ struct Options {
   bool emulate = false;    // STRAGGLAR_EMULATE=1: every rank on device 0, one cooperative launch
   bool const_fill = false; // STRAGGLAR_FILL=const: rank r holds r+1 everywhere (the reference's inputs)
   int verify = 2;          // STRAGGLAR_VERIFY = each (2) | last (1) | none (0)
+  int nvls = 0;            // STRAGGLAR_NVLS = 0 | 1 (buffers bound to NVLink multicast objects, required) | try
   std::string schedule_text;  // STRAGGLAR_SCHEDULE=<file with a synthesizer printout>
 };
 
@@ -71,7 +72,12 @@ inline Options read_options() {
   }
   o.dtype = dtype_from(env_str("STRAGGLAR_DTYPE", "float32"));
   o.straggler = (int)env_int("STRAGGLAR_STRAGGLER", -1);
-  o.path = !strcmp(env_str("STRAGGLAR_PATH", "tma"), "tma") ? SAR_PATH_TMA : SAR_PATH_SIMT;
+  {
+    const char* nv = env_str("STRAGGLAR_NVLS", "0");
+    o.nvls = !strcmp(nv, "try") ? 2 : (atoi(nv) != 0 ? 1 : 0);
+  }
+  // multimem instructions are issued by threads: with multicast buffers the simt path is the default
+  o.path = !strcmp(env_str("STRAGGLAR_PATH", o.nvls ? "simt" : "tma"), "tma") ? SAR_PATH_TMA : SAR_PATH_SIMT;
   o.blocks = (int)env_int("STRAGGLAR_BLOCKS", 0);
   o.threads = (int)env_int("STRAGGLAR_THREADS", 0);
   o.tile_bytes = (uint32_t)env_int("STRAGGLAR_TILE_BYTES", 0);
@@ -105,16 +111,25 @@ struct Buffers {
   std::vector<int> dev;
   std::vector<void*> ptr;
   std::vector<uint32_t*> result;  // per rank: 2 words for the verifier
-  void alloc(int n_, const std::vector<int>& devs, size_t bytes) {
-    n = n_; dev = devs; ptr.assign(n, nullptr); result.assign(n, nullptr);
+  sar_local_comm* owner = nullptr;
+  int mc_groups = 0;              // bit g: multicast group g serves the buffers
+  // mode: 0 plain device memory, 1 multicast required, 2 multicast when available (see sar_local_alloc)
+  void alloc(sar_local_comm* comm, int n_, const std::vector<int>& devs, size_t bytes, int mode = 0, uint32_t sub_members = 0) {
+    n = n_; dev = devs; ptr.assign(n, nullptr); result.assign(n, nullptr); owner = comm;
+    char err[512] = {0};
+    if (sar_local_alloc(comm, bytes, mode, sub_members, ptr.data(), err, sizeof err)) {
+      fprintf(stderr, "buffer allocation failed: %s\n", err);
+      exit(EXIT_FAILURE);
+    }
+    mc_groups = sar_local_multicast_groups(comm, ptr[0]);
     for (int r = 0; r < n; ++r) {
       CHECK_CUDA(cudaSetDevice(dev[r]));
-      CHECK_CUDA(cudaMalloc(&ptr[r], bytes < 16 ? 16 : bytes));
       CHECK_CUDA(cudaMalloc(&result[r], 8));
     }
   }
   void release() {
-    for (int r = 0; r < n; ++r) { cudaSetDevice(dev[r]); cudaFree(ptr[r]); cudaFree(result[r]); }
+    for (int r = 0; r < n; ++r) { cudaSetDevice(dev[r]); cudaFree(result[r]); }
+    if (owner && n) sar_local_free(owner, ptr[0]);
   }
 };
 

@@ -33,7 +33,8 @@ int main(int argc, char* argv[]) {
   sar_local_comm* comm = sar_local_create(n, devs.data(), o.emulate ? 1 : 0, err, sizeof err);
   if (!comm) { fprintf(stderr, "%s\n", err); exit(EXIT_FAILURE); }
   Buffers B;
-  B.alloc(n, devs, count * esize);
+  B.alloc(comm, n, devs, count * esize, o.nvls, 0);
+  if (o.nvls) fprintf(stderr, "multicast groups serving the buffers: %s\n", B.mc_groups & 1 ? "all ranks" : "none");
   sar_run_opts ro{};
   ro.path = o.path; ro.blocks = o.blocks; ro.threads = o.threads; ro.tile_bytes = o.tile_bytes;
   ro.timeout_s = o.timeout_s; ro.scale = 1.0f; ro.timed = 1;

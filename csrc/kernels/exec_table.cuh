@@ -69,10 +69,23 @@ __device__ __forceinline__ void st_vec(void* p, uint4 v) {
   asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// NVLink multicast (NVLS): the switch adds the 16-byte vectors of all members of the multicast
+// object, or stores one vector into all of them.
+__device__ __forceinline__ void mc_st_vec(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // ----------------------------------------------------------- element handling
 template <typename T> struct Vec;  // 16 bytes of T <-> floats
 template <> struct Vec<float> {
   static constexpr int N = 4;
+  __device__ static uint4 mc_ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
   __device__ static void unpack(uint4 v, float* f) {
     f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
   }
@@ -84,6 +97,12 @@ template <> struct Vec<float> {
 };
 template <> struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
+  __device__ static uint4 mc_ld_reduce(const void* p) {   // the switch accumulates in fp32 and rounds once
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
   __device__ static void unpack(uint4 v, float* f) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -110,6 +129,12 @@ template <> struct Vec<__nv_bfloat16> {
 };
 template <> struct Vec<__half> {
   static constexpr int N = 8;
+  __device__ static uint4 mc_ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
   __device__ static void unpack(uint4 v, float* f) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -336,6 +361,21 @@ __device__ void scalar_elems(const SarLaunchParams& P, const SarOp* op, uint64_t
   }
 }
 
+// The multicast view that serves this op in one instruction, or nullptr: a reduction over the own
+// slot and exactly the other members of a group (the switch adds all members' values), or a push
+// to exactly the other members (one multimem.st; it also rewrites the own slot with the value it
+// already holds).
+__device__ __forceinline__ char* mc_view_for(const SarLaunchParams& P, const SarOp* op) {
+  const bool reduce = op->kind == SAR_REDUCE && (op->flags & SAR_F_LOCAL);
+  if (!reduce && op->kind != SAR_PUSH) return nullptr;
+  if (!P.mc[0].base && !P.mc[1].base) return nullptr;
+  uint32_t mask = 1u << P.rank;
+  for (int q = 0; q < op->nsrc; ++q) mask |= 1u << op->src[q];
+  for (int g = 0; g < 2; ++g)
+    if (P.mc[g].base && P.mc[g].members == mask) return (char*)P.mc[g].base;
+  return nullptr;
+}
+
 // ------------------------------------------------------------------- simt path
 template <typename T, int UNROLL>
 __device__ void simt_tile(const SarLaunchParams& P, const Item& it) {
@@ -345,7 +385,54 @@ __device__ void simt_tile(const SarLaunchParams& P, const Item& it) {
   const uint64_t byte0 = it.elem0 * sizeof(T);
   char* own = (char*)P.comm.buf[P.rank] + byte0;
   const uint32_t tid = threadIdx.x, nth = blockDim.x;
-  if (op->kind == SAR_COPY || op->kind == SAR_PUSH) {
+  char* mcv = mc_view_for(P, op);
+  if (mcv) {
+    mcv += byte0;
+    if (op->kind == SAR_PUSH) {
+      // all destinations in one store through the switch
+      uint32_t v = tid;
+      for (; v + (UNROLL - 1) * nth < nvec; v += UNROLL * nth) {
+        uint4 r[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) r[u] = ld_vec_sys(own + (size_t)(v + u * nth) * 16);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) mc_st_vec(mcv + (size_t)(v + u * nth) * 16, r[u]);
+      }
+      for (; v < nvec; v += nth) mc_st_vec(mcv + (size_t)v * 16, ld_vec_sys(own + (size_t)v * 16));
+    } else {
+      // the switch loads every member's vector (the own one included) and returns the sum
+      const bool scaled = (op->flags & SAR_F_SCALE) != 0;
+      const float scale = P.scale;
+      uint32_t v = tid;
+      for (; v + (UNROLL - 1) * nth < nvec; v += UNROLL * nth) {
+        uint4 r[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) r[u] = Vec<T>::mc_ld_reduce(mcv + (size_t)(v + u * nth) * 16);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          if (scaled) {
+            float f[N];
+            Vec<T>::unpack(r[u], f);
+#pragma unroll
+            for (int i = 0; i < N; ++i) f[i] *= scale;
+            r[u] = Vec<T>::pack(f);
+          }
+          st_vec(own + (size_t)(v + u * nth) * 16, r[u]);
+        }
+      }
+      for (; v < nvec; v += nth) {
+        uint4 r = Vec<T>::mc_ld_reduce(mcv + (size_t)v * 16);
+        if (scaled) {
+          float f[N];
+          Vec<T>::unpack(r, f);
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[i] *= scale;
+          r = Vec<T>::pack(f);
+        }
+        st_vec(own + (size_t)v * 16, r);
+      }
+    }
+  } else if (op->kind == SAR_COPY || op->kind == SAR_PUSH) {
     const bool push = op->kind == SAR_PUSH;
     const char* src = push ? own : (const char*)P.comm.buf[op->src[0]] + byte0;
     const int ndst = push ? op->nsrc : 1;

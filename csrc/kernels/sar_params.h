@@ -11,6 +11,16 @@ struct SarDevComm {
   void* buf[SAR_MAX_RANKS];        // every rank's data buffer (same layout)
 };
 
+// An NVLink multicast (NVLS) view of the data buffers: `base` is this rank's mapping of a
+// multicast object to which the buffers of the ranks in `members` are bound at the same offsets,
+// so that one multimem.ld_reduce at base + x returns the sum of the members' values at x and one
+// multimem.st writes all of them.  base == nullptr: not available.
+struct SarMcGroup {
+  void* base;
+  uint32_t members;
+  uint32_t pad;
+};
+
 struct SarLaunchParams {
   SarDevComm comm;
   const SarOp* ops;
@@ -26,5 +36,6 @@ struct SarLaunchParams {
   uint32_t* status;       // first failure of this launch (0 = ok); may be mapped host memory
   uint64_t* trace;        // optional: [0] = arrival time, [1] = end time (%globaltimer ns), else nullptr
   uint64_t delay_ns;      // spin this long before arriving (a late rank when ranks share one launch)
+  SarMcGroup mc[2];       // multicast views (simt path): all ranks, and e.g. the non-stragglers
 };
 

@@ -11,6 +11,7 @@
 #include "../core/host_exec.h"
 #include "../kernels/sar_params.h"
 #include "../kernels/sar_cuda.h"
+#include "symm_alloc.h"
 
 namespace {
 struct DevTable { SarOp* ops = nullptr; uint16_t* round_begin = nullptr; uint32_t num_rounds = 0; };
@@ -33,7 +34,24 @@ struct sar_local_comm {
   std::vector<Rank> ranks;
   uint32_t epoch[SAR_NUM_CHANNELS] = {};
   SarLaunchParams* d_params = nullptr;   // emulate: n entries on devices[0]
+  std::vector<sar::SymmAlloc*> allocs;   // symmetric buffers handed out by sar_local_alloc
 };
+
+// The symmetric allocation that holds bufs[r] for every rank at one common offset, or nullptr.
+static const sar::SymmAlloc* find_alloc(const sar_local_comm* c, void* const* bufs, size_t bytes, size_t* offset) {
+  for (const sar::SymmAlloc* a : c->allocs) {
+    const char* b0 = (const char*)a->uc[0];
+    const char* p0 = (const char*)bufs[0];
+    if (p0 < b0 || p0 + bytes > b0 + a->mapped) continue;
+    const size_t off = (size_t)(p0 - b0);
+    bool same = true;
+    for (int r = 1; r < c->n && same; ++r) same = (const char*)bufs[r] == (const char*)a->uc[r] + off;
+    if (!same) continue;
+    *offset = off;
+    return a;
+  }
+  return nullptr;
+}
 
 #define CK(x)                                                                          \
   do {                                                                                 \
@@ -138,6 +156,7 @@ void sar_local_destroy(sar_local_comm* c) {
     if (!(c->emulate && r > 0)) cudaStreamDestroy(rk.stream);
   }
   if (c->d_params) { cudaSetDevice(c->ranks[0].dev); cudaFree(c->d_params); }
+  for (sar::SymmAlloc* a : c->allocs) { sar::symm_free(a); delete a; }
   delete c;
 }
 
@@ -165,6 +184,15 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
   std::vector<bool> delayed(n, false);
 
   for (int r = 0; r < n; ++r) c->ranks[r].timed = o->timed != 0;
+
+  // multicast views of the buffers, when they come from sar_local_alloc (simt path only: multimem
+  // instructions are issued by threads, not by the bulk-copy engine)
+  size_t mc_off = 0;
+  const sar::SymmAlloc* mc_alloc = nullptr;
+  if (!c->emulate && path == SAR_PATH_SIMT && !c->allocs.empty()) {
+    mc_alloc = find_alloc(c, bufs, (size_t)count * esize, &mc_off);
+    if (mc_alloc && !mc_alloc->mc_handle[0]) mc_alloc = nullptr;
+  }
 
   // ---- prepare every phase: geometry, device tables (uploaded on first use), launch parameters
   struct PhaseLaunch { std::vector<SarLaunchParams> hp; int blocks; uint32_t parts; };
@@ -203,6 +231,13 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       P.epoch_base = c->epoch[ch]; P.scale = o->scale; P.dtype = dtype;
       P.timeout_ns = (uint64_t)(timeout_s * 1e9);
       P.status = rk.status; P.trace = rk.trace;
+      if (mc_alloc) {
+        for (int g = 0; g < 2; ++g) {
+          if (!mc_alloc->mc[g][r]) continue;
+          P.mc[g].base = (char*)mc_alloc->mc[g][r] + mc_off;
+          P.mc[g].members = mc_alloc->members[g];
+        }
+      }
       P.delay_ns = 0;
       if (c->emulate && delay_ns && delay_ns[r] && !delayed[r] && (parts >> r & 1)) { P.delay_ns = delay_ns[r]; delayed[r] = true; }
     }
@@ -252,6 +287,53 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
     if (o->timed) CK(cudaEventRecord(rk.ev1, rk.stream));
   }
   return 0;
+}
+
+int sar_local_alloc(sar_local_comm* c, size_t bytes, int mode, uint32_t sub_members, void** bufs, char* err, int errlen) {
+  int devs[SAR_MAX_RANKS];
+  for (int r = 0; r < c->n; ++r) devs[r] = c->ranks[r].dev;
+  if (c->emulate) {
+    if (mode == sar::SYMM_MULTICAST) {
+      if (err) snprintf(err, errlen, "multicast needs one device per rank (the ranks are emulated on one device)");
+      return 1;
+    }
+    mode = sar::SYMM_PLAIN;
+  }
+  auto* a = new sar::SymmAlloc;
+  if (sar::symm_alloc(a, c->n, devs, bytes, mode, sub_members, err, errlen) != 0) { delete a; return 1; }
+  for (int r = 0; r < c->n; ++r) bufs[r] = a->uc[r];
+  c->allocs.push_back(a);
+  return 0;
+}
+
+int sar_local_free(sar_local_comm* c, void* buf0) {
+  for (size_t i = 0; i < c->allocs.size(); ++i) {
+    if (c->allocs[i]->uc[0] != buf0) continue;
+    sar::symm_free(c->allocs[i]);
+    delete c->allocs[i];
+    c->allocs.erase(c->allocs.begin() + (long)i);
+    return 0;
+  }
+  return 1;
+}
+
+int sar_local_multicast_groups(sar_local_comm* c, const void* buf0) {
+  for (const sar::SymmAlloc* a : c->allocs) {
+    const char* b0 = (const char*)a->uc[0];
+    if ((const char*)buf0 < b0 || (const char*)buf0 >= b0 + a->mapped) continue;
+    return (a->mc_handle[0] ? 1 : 0) | (a->mc_handle[1] ? 2 : 0);
+  }
+  return 0;
+}
+
+int sar_local_multicast_supported(sar_local_comm* c) {
+  if (c->emulate) return 0;
+  int devs[SAR_MAX_RANKS];
+  for (int r = 0; r < c->n; ++r) {
+    devs[r] = c->ranks[r].dev;
+    for (int q = 0; q < r; ++q) if (devs[q] == devs[r]) return 0;
+  }
+  return sar::multicast_supported(c->n, devs) ? 1 : 0;
 }
 
 uint32_t sar_local_sync(sar_local_comm* c, float* ms) {

@@ -44,6 +44,21 @@ uint32_t sar_local_sync(sar_local_comm* c, float* ms);
 // per rank: %globaltimer stamps {arrival, end} of the last phase it ran
 int sar_local_trace(sar_local_comm* c, uint64_t* out /* 2*n */);
 
+// Symmetric buffers: `bytes` on every rank's device, bufs[r] = rank r's.  mode 0: plain device
+// memory; 1: virtual-memory allocations bound to NVLink multicast objects (an error where the
+// devices or the driver do not offer multicast, or when the ranks share a device); 2: multicast
+// when available, else plain.  `sub_members` names the ranks of a second multicast group (e.g. the
+// non-stragglers; 0: none).  When a collective runs on the simt path over buffers that lie at the
+// same offset inside such an allocation, reductions over and pushes to all members of a group go
+// through the switch (multimem.ld_reduce / multimem.st) instead of one transfer per peer.
+int sar_local_alloc(sar_local_comm* c, size_t bytes, int mode, uint32_t sub_members, void** bufs, char* err, int errlen);
+// Frees the allocation whose rank-0 buffer is buf0 (after waiting for the devices).  0 if found.
+int sar_local_free(sar_local_comm* c, void* buf0);
+// Bit g set: multicast group g (0: all ranks, 1: sub_members) serves the allocation holding buf0.
+int sar_local_multicast_groups(sar_local_comm* c, const void* buf0);
+// 1 when every device of the communicator offers NVLink multicast (and the ranks do not share devices)
+int sar_local_multicast_supported(sar_local_comm* c);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,7 +22,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-Wno-nonnull"]
 CORE = [os.path.join(CSRC, "core", f) for f in ("plan.cpp", "host_exec.cpp", "c_api.cpp")]
 CUDA = [os.path.join(CSRC, "kernels", "exec_table.cu"), os.path.join(CSRC, "runtime", "local_comm.cu"),
-        os.path.join(CSRC, "kernels", "noalloc.cu")]
+        os.path.join(CSRC, "kernels", "noalloc.cu"), os.path.join(CSRC, "runtime", "symm_alloc.cu")]
 
 
 def nvcc() -> str:

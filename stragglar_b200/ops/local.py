@@ -39,6 +39,11 @@ def cuda_lib():
                                     C.POINTER(RunOpts), C.POINTER(C.c_uint64), C.c_char_p, C.c_int]
         L.sar_local_sync.restype, L.sar_local_sync.argtypes = C.c_uint32, [C.c_void_p, C.POINTER(C.c_float)]
         L.sar_local_trace.restype, L.sar_local_trace.argtypes = C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]
+        L.sar_local_alloc.restype = C.c_int
+        L.sar_local_alloc.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_uint32, C.POINTER(C.c_void_p), C.c_char_p, C.c_int]
+        L.sar_local_free.restype, L.sar_local_free.argtypes = C.c_int, [C.c_void_p, C.c_void_p]
+        L.sar_local_multicast_groups.restype, L.sar_local_multicast_groups.argtypes = C.c_int, [C.c_void_p, C.c_void_p]
+        L.sar_local_multicast_supported.restype, L.sar_local_multicast_supported.argtypes = C.c_int, [C.c_void_p]
         L.sar_cuda_delay.argtypes = [C.c_uint64, C.c_void_p]
         L.sar_cuda_fill_uniform.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_uint64, C.c_void_p]
         L.sar_cuda_fill_const.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_float, C.c_void_p]
@@ -172,6 +177,51 @@ class LocalComm:
         out = (C.c_uint64 * (2 * self.n))()
         _check(cuda_lib().sar_local_trace(self._h, out), "trace")
         return [(out[2 * r], out[2 * r + 1]) for r in range(self.n)]
+
+    # ---- symmetric buffers, optionally bound to NVLink multicast (NVLS) objects
+    MULTICAST_MODES = {False: 0, None: 0, "off": 0, True: 1, "require": 1, "try": 2}
+
+    def multicast_supported(self) -> bool:
+        """True when every device of the communicator offers NVLink multicast (one rank per device)."""
+        return bool(cuda_lib().sar_local_multicast_supported(self._h))
+
+    def alloc(self, numel: int, dtype=None, multicast="try", sub_members: int = 0):
+        """One buffer of ``numel`` elements per rank, as torch tensors that alias the allocation.
+
+        ``multicast``: ``False`` plain device memory; ``True`` virtual-memory allocations bound to a multicast
+        object over all ranks and, when ``sub_members`` (a rank bitmask) is given, to a second one over those ranks
+        -- an error where multicast is not available; ``"try"`` multicast when available, else plain.  On the simt
+        path, collectives on these tensors (or on equal slices of them) send reductions over, and pushes to, all
+        members of a group through the switch.  Free with :meth:`free` (or by closing the communicator); the
+        tensors must not be used afterwards."""
+        import torch
+        dtype = dtype or torch.float32
+        esize = torch.empty(0, dtype=dtype).element_size()
+        ptrs = (C.c_void_p * self.n)()
+        err = C.create_string_buffer(512)
+        rc = cuda_lib().sar_local_alloc(self._h, numel * esize, self.MULTICAST_MODES[multicast], sub_members, ptrs, err, 512)
+        if rc:
+            raise RuntimeError("symmetric allocation failed: " + err.value.decode())
+
+        class _Raw:   # what torch.as_tensor needs to alias device memory
+            def __init__(self, ptr, nbytes):
+                self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+        out = []
+        for r in range(self.n):
+            dev = self.devices[0] if self.emulate else self.devices[r]
+            raw = torch.as_tensor(_Raw(ptrs[r], max(numel * esize, 1)), device=f"cuda:{dev}")
+            out.append(raw[: numel * esize].view(dtype))
+        return out
+
+    def free(self, tensors) -> None:
+        """Releases an allocation made by :meth:`alloc` (pass the list it returned)."""
+        if cuda_lib().sar_local_free(self._h, C.c_void_p(tensors[0].data_ptr())):
+            raise ValueError("not an allocation of this communicator")
+
+    def multicast_groups(self, tensor) -> int:
+        """Bit 0: the multicast group of all ranks serves ``tensor``'s allocation; bit 1: the sub-group does."""
+        return cuda_lib().sar_local_multicast_groups(self._h, C.c_void_p(tensor.data_ptr()))
 
     def max_emulated_blocks(self, dtype_code: int = 0, path: str = "simt", threads: int = 0) -> int:
         return cuda_lib().sar_cuda_max_emulated_blocks(dtype_code, PATHS[path], threads)
