@@ -1,5 +1,5 @@
 #!/usr/bin/env bash
-# Reproduces the AllReduce sweeps of BASELINE.md section 4 on one 8-GPU box:
+# The full AllReduce comparison on one 8-GPU box:
 # this library (bin/allreduce), the unmodified reference programs (baseline/_ref)
 # and stock NCCL (bench/nccl_allreduce.py).  CSVs and a summary land in $OUT.
 #
@@ -19,6 +19,11 @@ SIZES=$SZ ALGS=stragglar,stragglar_a2a DELAYS=-1,5 run ours_n8_straggler2 STRAGG
 SIZES=$SZ ALGS=stragglar,stragglar_a2a,ring,rhd,direct DELAYS=-1,0,1,5,10 run ours_n4 STRAGGLAR_NGPUS=4
 SIZES=16777216,268435456,1073741824 ALGS=stragglar,stragglar_a2a,ring,direct DELAYS=5 run ours_n6 STRAGGLAR_NGPUS=6
 STRAGGLAR_WARMUP=$W bin/reducescatter 1073741824 $IT > "$OUT/ours_reducescatter.csv" 2> "$OUT/ours_reducescatter.err"
+# optional: buffers bound to NVLink multicast objects, in-switch reduction and replication (SWEEP_NVLS=1)
+if [ "${SWEEP_NVLS:-0}" = 1 ]; then
+  SIZES=$SZ ALGS=rsag,stragglar_a2a,stragglar DELAYS=-1,0,5 run ours_n8_nvls STRAGGLAR_NVLS=1
+  STRAGGLAR_NVLS=1 STRAGGLAR_WARMUP=$W bin/reducescatter 1073741824 $IT > "$OUT/ours_reducescatter_nvls.csv" 2> "$OUT/ours_reducescatter_nvls.err"
+fi
 
 # the reference's programs (sizes padded as its pad_buffers.py prescribes for 8 GPUs)
 if [ -x baseline/_ref/allreduce8 ]; then
