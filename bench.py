@@ -131,6 +131,8 @@ def run_reference(args) -> int:
                     "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                     "dtype": "fp32", "data": "constant fill (rank r holds r+1), as the reference program does",
                     "clocks": cs.summary(), "wall_s": wall,
+                    "e2e": {"unavailable": "the reference program fills its buffers on the device and reads nothing "
+                                           "back: it has no host path to time (stragglar/allreduce_8GPU.cu:1010-1020)"},
                     "config": {"model": f"allreduce {args.alg}", "bytes_per_gpu": nbytes, "delay_ms": args.delay_ms,
                                "timing": "device 0 events only (the reference's own clock), nominal delay subtracted",
                                "parallelism": f"1 process x {n} GPUs, NCCL send/recv"}})
