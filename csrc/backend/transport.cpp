@@ -31,6 +31,18 @@ Transport::Transport(bool cuda, int device, int rank, int n, size_t data_bytes, 
   staging_bytes_ = std::min(data_bytes_, (staging_bytes + 4095) / 4096 * 4096);
   total_bytes_ = ArenaLayout::kDataOff + data_bytes_;
   heap_ = std::make_shared<Heap>(heap_bytes());
+  try {
+    open_arenas(store, prefix);
+  } catch (...) {
+    // e.g. a peer that never published its handle: give back what was mapped so far
+    if (!shm_name_.empty()) shm_unlink(shm_name_.c_str());
+    release();
+    throw;
+  }
+}
+
+void Transport::open_arenas(const c10::intrusive_ptr<c10d::Store>& store, const std::string& prefix) {
+  const int rank = rank_, n = n_, device = device_;
   const std::string me = prefix + "/arena/" + std::to_string(rank);
   if (cuda_) {
     SAR_CUDA_CHECK(cudaSetDevice(device));
@@ -83,7 +95,9 @@ Transport::Transport(bool cuda, int device, int rank, int n, size_t data_bytes, 
   if (!cuda_) shm_unlink(shm_name_.c_str());   // the mappings keep the memory alive
 }
 
-Transport::~Transport() {
+Transport::~Transport() { release(); }
+
+void Transport::release() {
   if (cuda_) {
     cudaSetDevice(device_);
     cudaDeviceSynchronize();
@@ -94,6 +108,7 @@ Transport::~Transport() {
     for (int r = 0; r < n_; ++r)
       if (base_[r]) munmap(base_[r], total_bytes_);
   }
+  for (int r = 0; r < n_; ++r) base_[r] = nullptr;
 }
 
 int64_t Transport::heap_offset(const void* p, size_t bytes) const {

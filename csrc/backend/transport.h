@@ -78,6 +78,8 @@ class Transport {
   std::shared_ptr<Heap> heap() const { return heap_; }
 
  private:
+  void open_arenas(const c10::intrusive_ptr<c10d::Store>& store, const std::string& key_prefix);
+  void release();
   bool cuda_;
   int device_, rank_, n_;
   size_t data_bytes_, staging_bytes_, total_bytes_;

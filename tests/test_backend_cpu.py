@@ -290,3 +290,40 @@ def _subgroups(rank, world):
 
 def test_subgroups_and_odd_sizes():
     run_ranks(4, _subgroups)
+
+
+def _alone(port, errq):
+    """Rank 0 of a two-rank group whose other rank never starts."""
+    try:
+        import glob
+        from datetime import timedelta
+        sys.path.insert(0, ROOT)
+        import stragglar_b200.parallel  # noqa: F401
+        store = dist.TCPStore("127.0.0.1", port, 2, is_master=True, timeout=timedelta(seconds=2), wait_for_workers=False)
+        try:
+            dist.init_process_group("stragglar", store=store, rank=0, world_size=2, timeout=timedelta(seconds=2))
+            dist.all_reduce(torch.ones(8))       # the arenas are opened by the first collective at the latest
+            errq.put("a group with a missing rank came up")
+        except Exception as e:                   # the store gives up waiting for the peer's arena
+            if "imeout" not in str(e) and "wait" not in str(e).lower():
+                errq.put(f"unexpected error: {e!r}")
+        left = glob.glob(f"/dev/shm/sar_{os.getpid()}_*")
+        if left:
+            errq.put(f"shared memory left behind: {left}")
+    except Exception:
+        errq.put(traceback.format_exc())
+
+
+def test_rank_that_never_joins_fails_the_bootstrap_and_leaves_no_shared_memory():
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    p = ctx.Process(target=_alone, args=(_free_port(), errq))
+    p.start()
+    p.join(60)
+    msgs = []
+    while not errq.empty():
+        msgs.append(errq.get())
+    if p.is_alive():
+        p.kill()
+        msgs.append("the lone rank hung")
+    assert not msgs, "\n".join(msgs)
