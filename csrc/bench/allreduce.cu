@@ -37,6 +37,28 @@ static std::vector<std::string> split_list(const char* s) {
 }
 
 // One (size, algorithm, delay) configuration on an existing communicator.
+// Per rank: when each schedule round started and ended on it (microseconds after the first start of
+// any rank) and how long its items waited for their operands (summed over the items of the round).
+static void print_round_trace(sar_local_comm* comm, int n, const char* alg, size_t bytes, float delay) {
+  std::vector<uint64_t> tr((size_t)n * 3 * SAR_MAX_ROUNDS);
+  if (sar_local_round_trace(comm, tr.data())) return;
+  uint64_t t0 = UINT64_MAX;
+  for (int r = 0; r < n; ++r)
+    for (int k = 0; k < SAR_MAX_ROUNDS; ++k) t0 = std::min(t0, tr[((size_t)r * 3 + 0) * SAR_MAX_ROUNDS + k]);
+  fprintf(stderr, "round trace: %s, %zu bytes, delay %.1f ms; per round: [start .. end] us after the first start, (wait us summed over items)\n",
+          alg, bytes, delay);
+  for (int r = 0; r < n; ++r) {
+    fprintf(stderr, "  rank %d:", r);
+    for (int k = 0; k < SAR_MAX_ROUNDS; ++k) {
+      const uint64_t s = tr[((size_t)r * 3 + 0) * SAR_MAX_ROUNDS + k];
+      if (s == UINT64_MAX) continue;
+      const uint64_t e = tr[((size_t)r * 3 + 1) * SAR_MAX_ROUNDS + k], w = tr[((size_t)r * 3 + 2) * SAR_MAX_ROUNDS + k];
+      fprintf(stderr, " r%d [%.0f .. %.0f] (%.0f)", k, (s - t0) / 1e3, (e - t0) / 1e3, w / 1e3);
+    }
+    fprintf(stderr, "\n");
+  }
+}
+
 static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const std::vector<int>& devs, size_t bytes,
                       const char* alg, int numIters, float sleepTime, bool header) {
   const int n = o.ngpus;
@@ -122,6 +144,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const 
     }
     for (int r = 0; r < n; ++r) { CHECK_CUDA(cudaSetDevice(devs[r])); CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)sar_local_stream(comm, r))); }
 
+    ro.trace_rounds = (o.trace && iter == numIters - 1) ? 1 : 0;
     if (sar_local_run(comm, prog, B.ptr.data(), count, o.dtype, &ro, sleepTime > 0 ? delay_ns.data() : nullptr, err, sizeof err)) {
       fprintf(stderr, "launch failed: %s\n", err);
       exit(EXIT_FAILURE);
@@ -131,6 +154,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const 
       fprintf(stderr, "collective failed in iteration %d: %s\n", iter, status < 0x1000 ? sar_status_string(status) : cudaGetErrorString((cudaError_t)(status - 0x1000)));
       exit(2);
     }
+    if (ro.trace_rounds) print_round_trace(comm, n, alg, bytes, sleepTime);
     if (o.verify == 2 || (o.verify == 1 && iter == numIters - 1)) {
       for (int r = 0; r < n; ++r) {
         CHECK_CUDA(cudaSetDevice(devs[r]));

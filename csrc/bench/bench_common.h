@@ -46,6 +46,7 @@ struct Options {
   bool emulate = false;    // STRAGGLAR_EMULATE=1: every rank on device 0, one cooperative launch
   bool const_fill = false; // STRAGGLAR_FILL=const: rank r holds r+1 everywhere (the reference's inputs)
   int verify = 2;          // STRAGGLAR_VERIFY = each (2) | last (1) | none (0)
+  bool trace = false;      // STRAGGLAR_TRACE=1: per-round statistics of the last timed iteration on stderr
   int nvls = 0;            // STRAGGLAR_NVLS = 0 | 1 (buffers bound to NVLink multicast objects, required) | try
   std::string schedule_text;  // STRAGGLAR_SCHEDULE=<file with a synthesizer printout>
 };
@@ -83,6 +84,7 @@ inline Options read_options() {
   o.tile_bytes = (uint32_t)env_int("STRAGGLAR_TILE_BYTES", 0);
   o.timeout_s = env_int("STRAGGLAR_TIMEOUT_MS", 10000) / 1000.0;
   o.warmup = (int)env_int("STRAGGLAR_WARMUP", 10);
+  o.trace = env_int("STRAGGLAR_TRACE", 0) != 0;
   o.const_fill = !strcmp(env_str("STRAGGLAR_FILL", "uniform"), "const");
   const char* v = env_str("STRAGGLAR_VERIFY", "each");
   o.verify = !strcmp(v, "none") ? 0 : !strcmp(v, "last") ? 1 : 2;

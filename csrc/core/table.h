@@ -40,6 +40,11 @@
 #define SAR_MAX_RANKS 16
 #define SAR_MAX_CHUNKS 16
 #define SAR_MAX_OPS 256
+#define SAR_MAX_ROUNDS 64
+// Trace words of a launch (uint64, %globaltimer ns): [0] arrival, [1] end; with round tracing on,
+// three arrays of SAR_MAX_ROUNDS follow: first item started, last item announced, time spent
+// waiting for operands (summed over the items of the round).
+#define SAR_TRACE_WORDS (2 + 3 * SAR_MAX_ROUNDS)
 #define SAR_VER_STRIDE 32u
 #define SAR_NUM_CHANNELS 4               // independent flag/control sets (0: all ranks, 1: the non-stragglers)
 #define SAR_FLAG_CAPACITY (1u << 18)     // flags per rank and channel

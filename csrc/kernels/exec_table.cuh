@@ -200,7 +200,6 @@ struct Item {
 
 // Geometry of the table resolved once per launch into shared memory, so that
 // walking the items needs no 64-bit division.
-#define SAR_MAX_ROUNDS 64
 struct OpGeom {
   uint64_t elem0;      // first element of the op's first tile
   uint64_t elem_end;   // end of the op's chunk
@@ -304,6 +303,18 @@ struct ItemWalker {
 
 __device__ __forceinline__ bool op_reads_local(const SarOp* op) {
   return op->kind == SAR_REDUCE_PUSH || (op->kind == SAR_REDUCE && (op->flags & SAR_F_LOCAL));
+}
+
+// Per-round statistics (optional): when the first item of a round started, how long the items
+// of the round waited for their operands, when the last one was announced.
+__device__ __forceinline__ void trace_item_start(const SarLaunchParams& P, const SarOp* op, uint64_t t_begin, uint64_t t_ready) {
+  if (!P.trace_rounds || op->round >= SAR_MAX_ROUNDS) return;
+  atomicMin((unsigned long long*)&P.trace[2 + op->round], (unsigned long long)t_begin);
+  atomicAdd((unsigned long long*)&P.trace[2 + 2 * SAR_MAX_ROUNDS + op->round], (unsigned long long)(t_ready - t_begin));
+}
+__device__ __forceinline__ void trace_item_end(const SarLaunchParams& P, const SarOp* op) {
+  if (!P.trace_rounds || op->round >= SAR_MAX_ROUNDS) return;
+  atomicMax((unsigned long long*)&P.trace[2 + SAR_MAX_ROUNDS + op->round], (unsigned long long)globaltimer());
 }
 
 // Waits (one thread) until every operand of the item is ready.
@@ -594,8 +605,14 @@ __device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t
     if (threadIdx.x == 0) {
       Item it;
       if (!walk.next(&it)) s_state = 0;
-      else if (!wait_item_ready(P, it, w, &arrived)) s_state = -1;
-      else { s_item = it; s_state = 1; }
+      else {
+        const uint64_t t_begin = P.trace_rounds ? globaltimer() : 0;
+        if (!wait_item_ready(P, it, w, &arrived)) s_state = -1;
+        else {
+          if (P.trace_rounds) trace_item_start(P, it.op, t_begin, globaltimer());
+          s_item = it; s_state = 1;
+        }
+      }
     }
     __syncthreads();
     if (s_state != 1) break;
@@ -605,6 +622,7 @@ __device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t
     if (threadIdx.x == 0) {
       fence_sys();
       publish_item(P, it.op, it.fidx);
+      trace_item_end(P, it.op);
     }
   }
   __syncthreads();
@@ -755,7 +773,9 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         return true;
       };
       while (ok && walk.next(&it)) {
+        const uint64_t t_begin = P.trace_rounds ? globaltimer() : 0;
         if (!wait_item_ready(P, it, w, &arrived)) { ok = false; break; }
+        if (P.trace_rounds) trace_item_start(P, it.op, t_begin, globaltimer());
         fence_proxy_async_global();   // flags were acquired through the generic proxy; the copies use the async one
         const SarOp* op = it.op;
         const bool push_only = op->kind == SAR_PUSH;            // the only source is the own slot
@@ -925,6 +945,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         for (uint32_t i = 0; i < n; ++i) {
           const PendEntry& e = S.pend[(head + i) % kPendRing];
           publish_item(P, e.op, e.fidx);
+          trace_item_end(P, e.op);
         }
         head += n;
         st_release_cta(&S.pend_head, head);

@@ -21,7 +21,7 @@ struct Rank {
   uint32_t* flags = nullptr;   // SAR_NUM_CHANNELS * SAR_FLAG_CAPACITY
   SarCtrl* ctrl = nullptr;     // SAR_NUM_CHANNELS
   uint32_t* status = nullptr;  // 1 word
-  uint64_t* trace = nullptr;   // 2 words
+  uint64_t* trace = nullptr;   // SAR_TRACE_WORDS words
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool timed = false;
   std::map<std::pair<uint64_t, int>, DevTable> tables;   // keyed by the table's contents, not its address
@@ -115,8 +115,8 @@ sar_local_comm* sar_local_create(int n, const int* devices, int emulate, char* e
     CK(cudaMemset(rk.ctrl, 0, sizeof(SarCtrl) * SAR_NUM_CHANNELS));
     CK(cudaMalloc(&rk.status, 16));
     CK(cudaMemset(rk.status, 0, 16));
-    CK(cudaMalloc(&rk.trace, 16));
-    CK(cudaMemset(rk.trace, 0, 16));
+    CK(cudaMalloc(&rk.trace, sizeof(uint64_t) * SAR_TRACE_WORDS));
+    CK(cudaMemset(rk.trace, 0, sizeof(uint64_t) * SAR_TRACE_WORDS));
     CK(cudaEventCreate(&rk.ev0));
     CK(cudaEventCreate(&rk.ev1));
   }
@@ -230,7 +230,7 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       P.geom = g; P.rank = r; P.nranks = n; P.participants = parts;
       P.epoch_base = c->epoch[ch]; P.scale = o->scale; P.dtype = dtype;
       P.timeout_ns = (uint64_t)(timeout_s * 1e9);
-      P.status = rk.status; P.trace = rk.trace;
+      P.status = rk.status; P.trace = rk.trace; P.trace_rounds = o->trace_rounds ? 1u : 0u;
       if (mc_alloc) {
         for (int g = 0; g < 2; ++g) {
           if (!mc_alloc->mc[g][r]) continue;
@@ -240,6 +240,16 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       }
       P.delay_ns = 0;
       if (c->emulate && delay_ns && delay_ns[r] && !delayed[r] && (parts >> r & 1)) { P.delay_ns = delay_ns[r]; delayed[r] = true; }
+    }
+  }
+
+  if (o->trace_rounds) {
+    // start stamps begin at the maximum (they are lowered with atomicMin), the rest at zero
+    for (int r = 0; r < n; ++r) {
+      Rank& rk = c->ranks[r];
+      CK(cudaSetDevice(rk.dev));
+      CK(cudaMemsetAsync(rk.trace + 2, 0xff, sizeof(uint64_t) * SAR_MAX_ROUNDS, rk.stream));
+      CK(cudaMemsetAsync(rk.trace + 2 + SAR_MAX_ROUNDS, 0, sizeof(uint64_t) * 2 * SAR_MAX_ROUNDS, rk.stream));
     }
   }
 
@@ -285,6 +295,16 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       CK((cudaError_t)sar_cuda_launch(&launches[ph].hp[r], path, launches[ph].blocks, o->threads, rk.stream));
     }
     if (o->timed) CK(cudaEventRecord(rk.ev1, rk.stream));
+  }
+  return 0;
+}
+
+int sar_local_round_trace(sar_local_comm* c, uint64_t* out) {
+  for (int r = 0; r < c->n; ++r) {
+    cudaSetDevice(c->ranks[r].dev);
+    cudaError_t e = cudaMemcpy(out + (size_t)r * 3 * SAR_MAX_ROUNDS, c->ranks[r].trace + 2, sizeof(uint64_t) * 3 * SAR_MAX_ROUNDS,
+                               cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
   }
   return 0;
 }

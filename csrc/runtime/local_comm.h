@@ -23,6 +23,7 @@ struct sar_run_opts {
   double timeout_s;       // bound of every device-side wait (<= 0: 10 s)
   float scale;            // fused multiplier of the result
   int timed;              // 1: bracket every rank's work with events after a device-side start barrier
+  int trace_rounds;       // 1: keep per-round statistics of this run (see sar_local_round_trace)
 };
 
 // devices[r] is the CUDA device of rank r.  emulate != 0 places every rank on
@@ -43,6 +44,11 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
 uint32_t sar_local_sync(sar_local_comm* c, float* ms);
 // per rank: %globaltimer stamps {arrival, end} of the last phase it ran
 int sar_local_trace(sar_local_comm* c, uint64_t* out /* 2*n */);
+// Per rank and schedule round of the last run made with trace_rounds = 1 (all phases of the
+// program together): out[(r * 3 + k) * SAR_MAX_ROUNDS + round] with k = 0: %globaltimer ns when the
+// round's first item started (UINT64_MAX: the rank had none), 1: when its last item was announced,
+// 2: ns the round's items spent waiting for their operands, summed over the items.
+int sar_local_round_trace(sar_local_comm* c, uint64_t* out /* n * 3 * SAR_MAX_ROUNDS */);
 
 // Symmetric buffers: `bytes` on every rank's device, bufs[r] = rank r's.  mode 0: plain device
 // memory; 1: virtual-memory allocations bound to NVLink multicast objects (an error where the

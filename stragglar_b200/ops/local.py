@@ -21,7 +21,7 @@ PATHS = {"simt": 0, "tma": 1}
 
 class RunOpts(C.Structure):
     _fields_ = [("path", C.c_int), ("blocks", C.c_int), ("threads", C.c_int), ("tile_bytes", C.c_uint32),
-                ("timeout_s", C.c_double), ("scale", C.c_float), ("timed", C.c_int)]
+                ("timeout_s", C.c_double), ("scale", C.c_float), ("timed", C.c_int), ("trace_rounds", C.c_int)]
 
 
 def cuda_lib():
@@ -39,6 +39,7 @@ def cuda_lib():
                                     C.POINTER(RunOpts), C.POINTER(C.c_uint64), C.c_char_p, C.c_int]
         L.sar_local_sync.restype, L.sar_local_sync.argtypes = C.c_uint32, [C.c_void_p, C.POINTER(C.c_float)]
         L.sar_local_trace.restype, L.sar_local_trace.argtypes = C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]
+        L.sar_local_round_trace.restype, L.sar_local_round_trace.argtypes = C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]
         L.sar_local_alloc.restype = C.c_int
         L.sar_local_alloc.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_uint32, C.POINTER(C.c_void_p), C.c_char_p, C.c_int]
         L.sar_local_free.restype, L.sar_local_free.argtypes = C.c_int, [C.c_void_p, C.c_void_p]
@@ -142,8 +143,9 @@ class LocalComm:
 
     def run(self, program: Program, tensors, path: str = "simt", blocks: int = 0, threads: int = 0,
             tile_bytes: int = 0, scale: float = 1.0, delay_ms: Optional[Sequence[float]] = None,
-            timeout_s: float = 10.0, timed: bool = False) -> None:
-        """Enqueue ``program`` in place on ``tensors`` (one per rank)."""
+            timeout_s: float = 10.0, timed: bool = False, trace_rounds: bool = False) -> None:
+        """Enqueue ``program`` in place on ``tensors`` (one per rank).  ``trace_rounds`` keeps per-round
+        statistics of this run for :meth:`round_trace`."""
         if len(tensors) != self.n:
             raise ValueError(f"need {self.n} tensors")
         t0 = tensors[0]
@@ -154,7 +156,7 @@ class LocalComm:
             raise ValueError("program was freed")
         # program handles come from libsar_core.so; libsar_cuda.so is built from the same
         # sources and reads them through the same accessors
-        opts = RunOpts(PATHS[path], blocks, threads, tile_bytes, timeout_s, scale, int(timed))
+        opts = RunOpts(PATHS[path], blocks, threads, tile_bytes, timeout_s, scale, int(timed), int(trace_rounds))
         ptrs = (C.c_void_p * self.n)(*[t.data_ptr() for t in tensors])
         dl = (C.c_uint64 * self.n)(*[int(d * 1e6) for d in delay_ms]) if delay_ms is not None else None
         err = C.create_string_buffer(256)
@@ -222,6 +224,22 @@ class LocalComm:
     def multicast_groups(self, tensor) -> int:
         """Bit 0: the multicast group of all ranks serves ``tensor``'s allocation; bit 1: the sub-group does."""
         return cuda_lib().sar_local_multicast_groups(self._h, C.c_void_p(tensor.data_ptr()))
+
+    MAX_ROUNDS = 64
+
+    def round_trace(self):
+        """Per rank, the rounds it worked on in the last run made with ``trace_rounds=True``:
+        ``[{round: (start_ns, end_ns, wait_ns)}]`` -- %globaltimer stamps of the round's first item starting and
+        its last item being announced, and the time its items spent waiting for operands (summed over items)."""
+        m = self.MAX_ROUNDS
+        out = (C.c_uint64 * (self.n * 3 * m))()
+        _check(cuda_lib().sar_local_round_trace(self._h, out), "round_trace")
+        res = []
+        for r in range(self.n):
+            base = r * 3 * m
+            res.append({k: (out[base + k], out[base + m + k], out[base + 2 * m + k]) for k in range(m)
+                        if out[base + k] != 0xFFFFFFFFFFFFFFFF})
+        return res
 
     def max_emulated_blocks(self, dtype_code: int = 0, path: str = "simt", threads: int = 0) -> int:
         return cuda_lib().sar_cuda_max_emulated_blocks(dtype_code, PATHS[path], threads)

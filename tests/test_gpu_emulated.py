@@ -175,3 +175,35 @@ def test_helper_kernels():
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record(); ops.delay(5.0); t1.record(); torch.cuda.synchronize()
     assert 4.9 <= t0.elapsed_time(t1) < 7.0
+
+
+@pytest.mark.parametrize("path", ["simt", "tma"])
+def test_round_trace(path):
+    """Per-round statistics: every round of a rank's table shows up, starts before it ends, rounds end in order
+    on the straggler (its matchings are serial), and a run without tracing leaves the record untouched."""
+    from stragglar_b200 import ops
+    n, count = 4, 60_000
+    comm = ops.LocalComm(n, emulate=True)
+    prog = sc.compile_program("stragglar", n)
+    xs = _inputs(n, count, torch.float32)
+    want = torch.stack([x.double() for x in xs]).sum(0)
+    comm.run(prog, xs, path=path, blocks=2, tile_bytes=4096, timeout_s=5.0, trace_rounds=True)
+    comm.sync()
+    for x in xs:
+        torch.testing.assert_close(x.double(), want, **TOL[torch.float32])
+    tr = comm.round_trace()
+    assert len(tr) == n
+    for r in range(n):
+        want_rounds = set()
+        for t in prog.phases:
+            want_rounds |= {int(k) for k in t.ranks[r].ops["round"]}
+        assert set(tr[r]) == want_rounds, (r, sorted(tr[r]), sorted(want_rounds))
+        for k, (start, end, wait) in tr[r].items():
+            assert 0 < start <= end and wait < 5_000_000_000
+    ends = [tr[n - 1][k][1] for k in sorted(tr[n - 1])]
+    assert ends == sorted(ends)
+    before = comm.round_trace()
+    comm.run(prog, xs, path=path, blocks=2, tile_bytes=4096, timeout_s=5.0)
+    comm.sync()
+    assert comm.round_trace() == before
+    comm.close()
