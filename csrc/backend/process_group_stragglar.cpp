@@ -94,14 +94,31 @@ ProcessGroupStragglar::~ProcessGroupStragglar() {
   }
 }
 
-const sar::Program& ProcessGroupStragglar::program() {
-  const std::string key = opts_.alg + "/" + std::to_string(opts_.straggler);
+// "auto" picks per call: with a declared straggler the NVSwitch-native straggler-aware variant
+// (every rank moves exactly S bytes per direction and the pre-phase hides in the straggler's
+// delay); with none, the one-shot reduce-scatter + all-gather up to 512 MiB and the ring above,
+// which is where the two cross on an 8-GPU NVSwitch box.  The choice depends only on what every
+// rank knows (message size, declared straggler), so all ranks make the same one.
+std::string ProcessGroupStragglar::algorithm_for(size_t bytes) const {
+  if (opts_.alg != "auto") return opts_.alg;
+  const int n = getSize();
+  if (opts_.straggler >= 0 && n >= 2 && n % 2 == 0) return "stragglar_a2a";
+  return bytes < (512ull << 20) ? "rsag" : "ring";
+}
+
+const sar::Program& ProcessGroupStragglar::program(size_t bytes) {
+  std::string alg = algorithm_for(bytes);
+  static const char* const kKnown[] = {"stragglar", "stragglar_a2a", "ring", "rhd", "direct", "rsag"};
+  bool known = false;
+  for (const char* k : kKnown) known = known || alg == k;
+  TORCH_CHECK(known, "stragglar backend: unknown algorithm '", alg,
+              "' (stragglar, stragglar_a2a, ring, rhd, direct, rsag or auto)");
+  const std::string key = alg + "/" + std::to_string(opts_.straggler);
   auto it = programs_.find(key);
   if (it != programs_.end()) return it->second;
   sar::Schedule sched;
   const sar::Schedule* sp = nullptr;
   if (!opts_.schedule_text.empty()) { sched = sar::parse_schedule(opts_.schedule_text); sp = &sched; }
-  std::string alg = opts_.alg;
   try {
     return programs_.emplace(key, sar::build_program(alg, getSize(), true, opts_.straggler, sp)).first->second;
   } catch (const std::exception& e) {
@@ -327,8 +344,8 @@ void ProcessGroupStragglar::allreduce_impl(Side& s, at::Tensor& tensor, float sc
   const int cdc = dtype_code(cdt);
   const uint64_t count = (uint64_t)tensor.numel();
   if (count == 0) return;
-  const sar::Program& prog = program();
   const size_t csize = cdc == SAR_F32 ? 4 : 2;
+  const sar::Program& prog = program(count * csize);
   char* ptr = (char*)tensor.data_ptr();
   const int64_t hoff = (cdt == tdt) ? t.heap_offset(ptr, count * csize) : -1;
   if (hoff >= 0 && (((uintptr_t)ptr) & 15) == 0) {
@@ -415,7 +432,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::reduce(std::vector<at::Ten
   for (uint64_t off = 0; off < (uint64_t)x.numel(); off += piece) {
     const uint64_t k = std::min<uint64_t>(piece, x.numel() - off);
     copy_local(s, stage, (char*)x.data_ptr() + off * es, k * es);
-    run_program(s, program(), t.staging_off(), k, x.scalar_type(), scale);
+    run_program(s, program((size_t)x.numel() * es), t.staging_off(), k, x.scalar_type(), scale);
     if (getRank() == opts.rootRank) copy_local(s, (char*)x.data_ptr() + off * es, stage, k * es);
   }
   finish(s, w);
@@ -826,6 +843,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_algorithm", [](const c10::intrusive_ptr<c10d::Backend>& b, const std::string& a) { cast(b)->set_algorithm(a); });
   m.def("get_straggler", [](const c10::intrusive_ptr<c10d::Backend>& b) { return cast(b)->straggler(); });
   m.def("get_algorithm", [](const c10::intrusive_ptr<c10d::Backend>& b) { return cast(b)->algorithm(); });
+  m.def("algorithm_for", [](const c10::intrusive_ptr<c10d::Backend>& b, size_t bytes) { return cast(b)->algorithm_for(bytes); });
   m.def("check_status", [](const c10::intrusive_ptr<c10d::Backend>& b, bool cuda) { return cast(b)->check_status(cuda); },
         py::arg("backend"), py::arg("cuda") = true, py::call_guard<py::gil_scoped_release>());
   m.def("launches", [](const c10::intrusive_ptr<c10d::Backend>& b) { return cast(b)->launches(); });

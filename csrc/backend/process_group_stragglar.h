@@ -39,7 +39,7 @@
 namespace sarpg {
 
 struct BackendOptions {
-  std::string alg = "stragglar";   // stragglar | stragglar_a2a | ring | rhd | direct | rsag
+  std::string alg = "stragglar";   // stragglar | stragglar_a2a | ring | rhd | direct | rsag | auto
   int straggler = -1;              // physical rank that is persistently late (-1: the last rank)
   int path = 1;                    // 0 simt, 1 tma
   int blocks = 0, threads = 0;
@@ -124,6 +124,8 @@ class ProcessGroupStragglar : public c10d::Backend {
   void set_algorithm(const std::string& alg);
   int straggler() const { return opts_.straggler; }
   std::string algorithm() const { return opts_.alg; }
+  // The algorithm an AllReduce of `bytes` runs: the configured one, or the choice of "auto".
+  std::string algorithm_for(size_t bytes) const;
   // Waits for the communication stream and returns the device status word
   // (a SarStatus; 0 = ok), clearing a recorded failure.
   int64_t check_status(bool cuda);
@@ -143,7 +145,7 @@ class ProcessGroupStragglar : public c10d::Backend {
   };
   Side& side(const at::Tensor& like);
   Side& side(bool cuda, int device);
-  const sar::Program& program();
+  const sar::Program& program(size_t bytes = 0);
   void run_program(Side& s, const sar::Program& prog, size_t data_off, uint64_t count, at::ScalarType dtype, float scale);
   void device_barrier(Side& s);
   c10::intrusive_ptr<WorkStragglar> begin(Side& s, c10d::OpType op, std::vector<at::Tensor> outputs);

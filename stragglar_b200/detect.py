@@ -120,6 +120,14 @@ class OnlineDetector:
         r, c = Counter(self.history).most_common(1)[0]
         return r if c >= self.threshold * len(self.history) else None
 
+    def no_straggler(self, release: float = 0.5) -> bool:
+        """True once the window is full and no rank was the straggler in ``release`` of it: the last-to-arrive
+        rank keeps changing, i.e. nobody is persistently late.  (Lower than ``threshold`` on purpose: between the
+        two fractions the current choice stands.)"""
+        if len(self.history) < self.window:
+            return False
+        return Counter(self.history).most_common(1)[0][1] < release * len(self.history)
+
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="find the persistent straggler in a training log")

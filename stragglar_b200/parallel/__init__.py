@@ -74,6 +74,17 @@ def get_straggler(device="cuda", group=None) -> int:
     return _ext().get_straggler(backend_of(device, group))
 
 
+def get_algorithm(device="cuda", group=None) -> str:
+    return _ext().get_algorithm(backend_of(device, group))
+
+
+def algorithm_for(nbytes: int, device="cuda", group=None) -> str:
+    """The algorithm an AllReduce of ``nbytes`` runs with: the configured one, or what ``"auto"`` picks --
+    ``stragglar_a2a`` while a straggler is declared (``set_straggler(r)``, ``r >= 0``), otherwise the one-shot
+    reduce-scatter + all-gather below 512 MiB and the ring above."""
+    return _ext().algorithm_for(backend_of(device, group), int(nbytes))
+
+
 def empty_symmetric(numel: int, dtype=None, device="cuda", group=None):
     """A 1-D tensor in the backend's symmetric heap.  Collective: every rank
     must call it with the same sizes in the same order."""
@@ -120,7 +131,10 @@ class StragglerMonitor:
     a sliding window by :class:`stragglar_b200.detect.OnlineDetector`.  When a
     rank has been the straggler in ``threshold`` of the last ``window`` steps
     and differs from the current choice, ``set_straggler`` is applied on all
-    ranks at the same step (every rank sees the same gathered times)."""
+    ranks at the same step (every rank sees the same gathered times).  With
+    ``alg="auto"`` the monitor also withdraws the declaration once no rank is
+    the straggler in at least half of the window, which sends the group back
+    to the straggler-free algorithms."""
 
     def __init__(self, window: int = 20, threshold: float = 0.8, device="cuda", group=None):
         import torch.distributed as dist
@@ -138,10 +152,15 @@ class StragglerMonitor:
         dist.all_gather(allv, mine, group=self.group)
         self.detector.update([float(v.item()) for v in allv])
         rec = self.detector.recommendation()
-        cur = get_straggler(self.device, self.group)
-        cur = world - 1 if cur < 0 else cur
+        raw = get_straggler(self.device, self.group)
+        auto = get_algorithm(self.device, self.group) == "auto"
+        # -1 is "the last rank" for the StragglAR algorithms and "nobody" for "auto"
+        cur = raw if (auto or raw >= 0) else world - 1
         if rec is not None and rec != cur:
             set_straggler(rec, self.device, self.group)
+            self.changes += 1
+        elif auto and raw >= 0 and self.detector.no_straggler():
+            set_straggler(-1, self.device, self.group)     # nobody is persistently late any more
             self.changes += 1
         return rec
 

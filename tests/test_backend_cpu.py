@@ -327,3 +327,44 @@ def test_rank_that_never_joins_fails_the_bootstrap_and_leaves_no_shared_memory()
         p.kill()
         msgs.append("the lone rank hung")
     assert not msgs, "\n".join(msgs)
+
+
+def _auto(rank, world):
+    import stragglar_b200.parallel as sp
+    dev = "cpu"
+    sp.set_algorithm("auto", dev)
+    assert sp.get_algorithm(dev) == "auto" and sp.get_straggler(dev) == -1
+    # nobody declared late: one-shot reduce-scatter + all-gather for small messages, the ring for large ones
+    assert sp.algorithm_for(1 << 20, dev) == "rsag" and sp.algorithm_for(1 << 30, dev) == "ring"
+    x = _seeded(rank, 5000)
+    want = sum(_seeded(r, 5000) for r in range(world))
+    dist.all_reduce(x)
+    torch.testing.assert_close(x, want, atol=1e-5, rtol=1e-6)
+    # a declared straggler switches to the straggler-aware variant, whatever the size
+    sp.set_straggler(1, dev)
+    assert sp.algorithm_for(1 << 20, dev) == "stragglar_a2a" == sp.algorithm_for(1 << 30, dev)
+    y = _seeded(rank, 5000)
+    dist.all_reduce(y)
+    torch.testing.assert_close(y, want, atol=1e-5, rtol=1e-6)
+    # the monitor withdraws the declaration when the last rank to arrive keeps changing
+    mon = sp.StragglerMonitor(window=4, threshold=0.75, device=dev)
+    fake = iter([[5, 1, 5, 5], [1, 5, 5, 5], [5, 5, 1, 5], [5, 5, 5, 1]])
+    real = sp.last_collective_ms
+    try:
+        for times in fake:
+            sp.last_collective_ms = lambda *a, _t=times, **k: float(_t[rank])
+            mon.step()
+    finally:
+        sp.last_collective_ms = real
+    assert sp.get_straggler(dev) == -1 and mon.changes == 1
+    assert sp.algorithm_for(1 << 20, dev) == "rsag"
+    # a fixed algorithm is returned as configured; an unknown name is refused and changes nothing
+    sp.set_algorithm("ring", dev)
+    assert sp.algorithm_for(123, dev) == "ring"
+    with pytest.raises(RuntimeError, match="unknown algorithm"):
+        sp.set_algorithm("tree", dev)
+    assert sp.get_algorithm(dev) == "ring"
+
+
+def test_auto_algorithm_selection():
+    run_ranks(4, _auto)

@@ -131,3 +131,17 @@ def test_detect_cli_writes_the_delay_cdf(tmp_path, capsys):
     assert rows[0] == "delay_ms,fraction"
     pts = [tuple(map(float, r.split(","))) for r in rows[1:]]
     assert pts == sorted(pts) and pts[-1][1] == 1.0 and len(pts) == 3
+
+
+def test_online_detector_reports_when_nobody_is_persistently_late():
+    d = detect.OnlineDetector(4, window=4, threshold=0.75)
+    for times in ([9, 1, 9, 9], [9, 1, 9, 9], [9, 1, 9, 9]):
+        d.update(times)
+    assert not d.no_straggler()              # the window is not full yet
+    d.update([9, 1, 9, 9])
+    assert d.recommendation() == 1 and not d.no_straggler()
+    for times in ([1, 9, 9, 9], [9, 9, 1, 9], [9, 9, 9, 1]):
+        d.update(times)
+    assert d.recommendation() is None and d.no_straggler()
+    d.update([9, 9, 9, 1]); d.update([9, 9, 9, 1])
+    assert d.recommendation() is None and not d.no_straggler()   # between the two fractions nothing changes
