@@ -143,5 +143,5 @@ def test_online_detector_reports_when_nobody_is_persistently_late():
     for times in ([1, 9, 9, 9], [9, 9, 1, 9], [9, 9, 9, 1]):
         d.update(times)
     assert d.recommendation() is None and d.no_straggler()
-    d.update([9, 9, 9, 1]); d.update([9, 9, 9, 1])
+    d.update([9, 9, 9, 1])
     assert d.recommendation() is None and not d.no_straggler()   # between the two fractions nothing changes
