@@ -181,6 +181,9 @@ def main() -> int:
         return 2
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29533")
+    # host threads and pinned buffers on the CPUs next to this rank's GPU (matters for the end-to-end copies)
+    from stragglar_b200.utils.affinity import bind_to_gpu
+    bound = bind_to_gpu(local)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dtype = getattr(torch, args.dtype)
@@ -286,7 +289,7 @@ def main() -> int:
         ms_e2e, _ = timed(e2e_step, e2e_steps)
         e2e = {"value": world * nbytes / 1e9 / ((ms_e2e - real_delay) / 1e3), "unit": "GB/s",
                "ms_per_step": ms_e2e, "steps": e2e_steps, "h2d_bytes_per_step": nbytes,
-               "d2h_bytes_per_step": back * esize,
+               "d2h_bytes_per_step": back * esize, "host_cpus_bound": len(bound) if bound else None,
                "path": "pinned host -> symmetric device tensor -> dist.all_reduce(op=AVG) -> 4 KiB of the result back"}
 
     # the NVSwitch-native variant of the same collective, device-timed the same way

@@ -74,6 +74,8 @@ def main() -> int:
     os.environ.setdefault("MASTER_PORT", "29500")
     cuda = not args.cpu
     if cuda:
+        from stragglar_b200.utils.affinity import bind_to_gpu
+        bind_to_gpu(local)                 # host threads and pinned batches next to this rank's GPU
         torch.cuda.set_device(local)
     dev = torch.device("cuda", local) if cuda else torch.device("cpu")
     straggler = args.straggler if args.straggler >= 0 else world - 1

@@ -145,3 +145,37 @@ def test_online_detector_reports_when_nobody_is_persistently_late():
     assert d.recommendation() is None and d.no_straggler()
     d.update([9, 9, 9, 1])
     assert d.recommendation() is None and not d.no_straggler()   # between the two fractions nothing changes
+
+
+def test_cpu_affinity_from_a_fake_nvml(monkeypatch):
+    import os
+
+    from stragglar_b200.utils import affinity
+
+    assert affinity.cpus_from_masks([0b1011, 0b1]) == [0, 1, 3, 64]
+
+    class FakeNvml:
+        def __init__(self, masks):
+            self.masks, self.calls = masks, []
+        def nvmlInit(self): self.calls.append("init")
+        def nvmlShutdown(self): self.calls.append("shutdown")
+        def nvmlDeviceGetHandleByIndex(self, i): self.calls.append(("handle", i)); return i
+        def nvmlDeviceGetCpuAffinity(self, h, words): return self.masks
+
+    mine = sorted(os.sched_getaffinity(0))
+    keep = mine[: max(1, len(mine) // 2)]
+    mask = 0
+    for c in keep:
+        mask |= 1 << c
+    words = [(mask >> (64 * i)) & (2**64 - 1) for i in range(max(keep) // 64 + 1)]
+    try:
+        monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "4,5")
+        fake = FakeNvml(words)
+        assert affinity.bind_to_gpu(1, fake) == keep and sorted(os.sched_getaffinity(0)) == keep
+        assert ("handle", 5) in fake.calls and fake.calls[-1] == "shutdown"
+        # CPUs the process may not use, or no answer at all: nothing changes
+        assert affinity.bind_to_gpu(0, FakeNvml([0, 0, 0, 1 << 62])) is None
+        assert affinity.bind_to_gpu(0, object()) is None
+        assert sorted(os.sched_getaffinity(0)) == keep
+    finally:
+        os.sched_setaffinity(0, mine)
