@@ -87,6 +87,31 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(self.rows)}
 
 
+def reference_backend_e2e(args) -> dict:
+    """The end-to-end step through the reference's own c10d backend (baseline/ref_backend_e2e.py), run as eight
+    processes of its own.  Opt-in (STRAGGLAR_REF_E2E=1): the backend is written for exactly 8 ranks."""
+    script = os.path.join(ROOT, "baseline", "ref_backend_e2e.py")
+    port = 20000 + (os.getpid() % 20000)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "8", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), script, "--steps", str(max(3, min(args.steps, 10))), "--warmup", "3",
+           "--delay-ms", str(args.delay_ms)]
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_PORT", "MASTER_ADDR", "GROUP_RANK", "ROLE_RANK",
+                        "LOCAL_WORLD_SIZE", "ROLE_WORLD_SIZE", "TORCHELASTIC_RUN_ID")}
+    try:
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference backend did not finish its end-to-end steps within 600 s"}
+    for line in reversed(p.stdout.splitlines()):
+        line = line.strip()
+        if line.startswith("{") and "ms_per_step" in line:
+            try:
+                return json.loads(line)
+            except ValueError:
+                pass
+    return {"unavailable": f"the reference backend run exited {p.returncode}: {(p.stderr or p.stdout)[-200:]!r}"}
+
+
 def run_reference(args) -> int:
     """The reference arm: the unmodified stragglar/allreduce_{4,8}GPU.cu
     program, built with nvcc as its README says, run by rank 0 on all N GPUs
@@ -124,6 +149,10 @@ def run_reference(args) -> int:
             out["unavailable"] = f"reference program exited {p.returncode}: {(p.stderr or p.stdout)[-200:]!r}"
             print(json.dumps(out), flush=True)
             return 0
+        e2e = {"unavailable": "the reference program fills its buffers on the device and reads nothing back: it has "
+                              "no host path to time (stragglar/allreduce_8GPU.cu:1010-1020)"}
+        if os.environ.get("STRAGGLAR_REF_E2E", "0") == "1" and n == 8 and args.alg == "stragglar":
+            e2e = reference_backend_e2e(args)
         ms = statistics.mean(float(r[4]) for r in rows)
         delay = max(args.delay_ms, 0.0)
         value = n * nbytes / 1e9 / ((ms - delay) / 1e3)
@@ -131,8 +160,7 @@ def run_reference(args) -> int:
                     "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                     "dtype": "fp32", "data": "constant fill (rank r holds r+1), as the reference program does",
                     "clocks": cs.summary(), "wall_s": wall,
-                    "e2e": {"unavailable": "the reference program fills its buffers on the device and reads nothing "
-                                           "back: it has no host path to time (stragglar/allreduce_8GPU.cu:1010-1020)"},
+                    "e2e": e2e,
                     "config": {"model": f"allreduce {args.alg}", "bytes_per_gpu": nbytes, "delay_ms": args.delay_ms,
                                "timing": "device 0 events only (the reference's own clock), nominal delay subtracted",
                                "parallelism": f"1 process x {n} GPUs, NCCL send/recv"}})
