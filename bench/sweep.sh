@@ -22,6 +22,7 @@ STRAGGLAR_WARMUP=$W bin/reducescatter 1073741824 $IT > "$OUT/ours_reducescatter.
 # optional: buffers bound to NVLink multicast objects, in-switch reduction and replication (SWEEP_NVLS=1)
 if [ "${SWEEP_NVLS:-0}" = 1 ]; then
   SIZES=$SZ ALGS=rsag,stragglar_a2a,stragglar DELAYS=-1,0,5 run ours_n8_nvls STRAGGLAR_NVLS=1
+  SIZES=$SZ ALGS=rsag,stragglar_a2a,stragglar DELAYS=-1,0,5 run ours_n8_nvls_simta STRAGGLAR_NVLS=1 STRAGGLAR_PATH=simta
   STRAGGLAR_NVLS=1 STRAGGLAR_WARMUP=$W bin/reducescatter 1073741824 $IT > "$OUT/ours_reducescatter_nvls.csv" 2> "$OUT/ours_reducescatter_nvls.err"
 fi
 

@@ -78,7 +78,7 @@ ProcessGroupStragglar::ProcessGroupStragglar(const c10::intrusive_ptr<c10d::Stor
   prefix_ = "sar";
   if (const char* a = getenv("STRAGGLAR_ALG")) if (*a) opts_.alg = a;
   if (const char* s = getenv("STRAGGLAR_STRAGGLER")) if (*s) opts_.straggler = atoi(s);
-  if (const char* p = getenv("STRAGGLAR_PATH")) if (*p) opts_.path = !strcmp(p, "simt") ? SAR_PATH_SIMT : SAR_PATH_TMA;
+  if (const char* p = getenv("STRAGGLAR_PATH")) if (*p) opts_.path = !strcmp(p, "simt") ? SAR_PATH_SIMT : !strcmp(p, "simta") ? SAR_PATH_SIMTA : SAR_PATH_TMA;
   if (const char* b = getenv("STRAGGLAR_BLOCKS")) if (*b) opts_.blocks = atoi(b);
   if (const char* b = getenv("STRAGGLAR_THREADS")) if (*b) opts_.threads = atoi(b);
   if (const char* b = getenv("STRAGGLAR_TILE_BYTES")) if (*b) opts_.tile_bytes = (uint32_t)atoi(b);
@@ -806,7 +806,11 @@ static c10::intrusive_ptr<c10d::Backend> create_backend(const c10::intrusive_ptr
   BackendOptions o;
   if (options.contains("alg")) o.alg = options["alg"].cast<std::string>();
   if (options.contains("straggler")) o.straggler = options["straggler"].cast<int>();
-  if (options.contains("path")) o.path = options["path"].cast<std::string>() == "simt" ? SAR_PATH_SIMT : SAR_PATH_TMA;
+  if (options.contains("path")) {
+    const std::string p = options["path"].cast<std::string>();
+    TORCH_CHECK(p == "simt" || p == "tma" || p == "simta", "stragglar backend: unknown path '", p, "' (simt, tma or simta)");
+    o.path = p == "simt" ? SAR_PATH_SIMT : p == "simta" ? SAR_PATH_SIMTA : SAR_PATH_TMA;
+  }
   if (options.contains("blocks")) o.blocks = options["blocks"].cast<int>();
   if (options.contains("threads")) o.threads = options["threads"].cast<int>();
   if (options.contains("tile_bytes")) o.tile_bytes = options["tile_bytes"].cast<uint32_t>();

@@ -41,7 +41,7 @@ namespace sarpg {
 struct BackendOptions {
   std::string alg = "stragglar";   // stragglar | stragglar_a2a | ring | rhd | direct | rsag | auto
   int straggler = -1;              // physical rank that is persistently late (-1: the last rank)
-  int path = 1;                    // 0 simt, 1 tma
+  int path = 1;                    // 0 simt, 1 tma, 2 simta (see SarPath)
   int blocks = 0, threads = 0;
   uint32_t tile_bytes = 0;
   double timeout_s = 30.0;         // bound of every device-side wait

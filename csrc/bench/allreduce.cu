@@ -191,7 +191,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const 
     const double busbw = algbw * 2.0 * (n - 1) / std::max(n, 1);
     const double roof_ms = link_bytes / (link_gbs * 1e9) * 1e3;
     printf("%s,%zu,%d,%.3f,%.3f,%.3f,%d,%s,%s,%.1f,%.2f,%.2f,%.3f,%.3f\n", alg, (size_t)count * esize, iter + 1, sleepTime, t, bw, n,
-           dtype_name(o.dtype), o.path == SAR_PATH_TMA ? "tma" : (B.mc_groups ? "simt+nvls" : "simt"), t * 1e3, algbw, busbw, net_ms > 0 ? roof_ms / net_ms : 0.0, real_delay_ms);
+           dtype_name(o.dtype), path_label(o.path, B.mc_groups), t * 1e3, algbw, busbw, net_ms > 0 ? roof_ms / net_ms : 0.0, real_delay_ms);
   }
   sar_program_free(prog);
   if (post) sar_program_free(post);
@@ -230,7 +230,7 @@ int main(int argc, char* argv[]) {
     const uint32_t all = (n >= 32) ? 0xffffffffu : ((1u << n) - 1u);
     B.alloc(comm, n, devs, max_bytes, o.nvls, all & ~(1u << straggler));
     if (o.nvls) fprintf(stderr, "multicast groups serving the buffers: %s%s%s\n", B.mc_groups & 1 ? "all ranks" : "none",
-                        B.mc_groups & 2 ? ", non-stragglers" : "", o.path == SAR_PATH_SIMT ? "" : " (unused: the path is not simt)");
+                        B.mc_groups & 2 ? ", non-stragglers" : "", o.path != SAR_PATH_TMA ? "" : " (unused: the bulk-copy path does not issue multimem instructions)");
   }
   int failures = 0;
   bool header = true;

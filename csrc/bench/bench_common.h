@@ -38,7 +38,7 @@ struct Options {
   int ngpus = 0;           // STRAGGLAR_NGPUS (default: all visible, at most 8)
   int dtype = SAR_F32;     // STRAGGLAR_DTYPE = float32 | bfloat16 | float16
   int straggler = -1;      // STRAGGLAR_STRAGGLER: physical rank that is late (default n-1)
-  int path = SAR_PATH_SIMT;// STRAGGLAR_PATH = simt | tma
+  int path = SAR_PATH_SIMT;// STRAGGLAR_PATH = simt | tma | simta
   int blocks = 0, threads = 0;
   uint32_t tile_bytes = 0;
   double timeout_s = 10.0; // STRAGGLAR_TIMEOUT_MS
@@ -57,6 +57,19 @@ inline int dtype_from(const char* s) {
   if (!strcmp(s, "float16") || !strcmp(s, "fp16") || !strcmp(s, "half")) return SAR_F16;
   fprintf(stderr, "Invalid dtype: %s\n", s);
   exit(EXIT_FAILURE);
+}
+inline int path_from(const char* s) {
+  if (!strcmp(s, "tma")) return SAR_PATH_TMA;
+  if (!strcmp(s, "simt")) return SAR_PATH_SIMT;
+  if (!strcmp(s, "simta")) return SAR_PATH_SIMTA;
+  fprintf(stderr, "Invalid path: %s (simt, tma or simta)\n", s);
+  exit(EXIT_FAILURE);
+}
+// path column of the CSV; "+nvls" when multicast views serve the buffers
+inline const char* path_label(int path, int mc_groups) {
+  if (path == SAR_PATH_TMA) return "tma";
+  if (path == SAR_PATH_SIMTA) return mc_groups ? "simta+nvls" : "simta";
+  return mc_groups ? "simt+nvls" : "simt";
 }
 inline const char* dtype_name(int d) { return d == SAR_F32 ? "float32" : d == SAR_BF16 ? "bfloat16" : "float16"; }
 inline uint32_t dtype_size(int d) { return d == SAR_F32 ? 4 : 2; }
@@ -78,7 +91,7 @@ inline Options read_options() {
     o.nvls = !strcmp(nv, "try") ? 2 : (atoi(nv) != 0 ? 1 : 0);
   }
   // multimem instructions are issued by threads: with multicast buffers the simt path is the default
-  o.path = !strcmp(env_str("STRAGGLAR_PATH", o.nvls ? "simt" : "tma"), "tma") ? SAR_PATH_TMA : SAR_PATH_SIMT;
+  o.path = path_from(env_str("STRAGGLAR_PATH", o.nvls ? "simt" : "tma"));
   o.blocks = (int)env_int("STRAGGLAR_BLOCKS", 0);
   o.threads = (int)env_int("STRAGGLAR_THREADS", 0);
   o.tile_bytes = (uint32_t)env_int("STRAGGLAR_TILE_BYTES", 0);

@@ -18,6 +18,12 @@ __global__ void __launch_bounds__(tma::kThreads, 1) sar_exec_tma_kernel(const __
   run_rank_tma<T>(P, blockIdx.x, gridDim.x, *reinterpret_cast<tma::Shared*>(sar_smem));
 }
 
+template <typename T>
+__global__ void __launch_bounds__(simta::kThreads, 1) sar_exec_simta_kernel(const __grid_constant__ SarLaunchParams P) {
+  __shared__ simta::Shared S;
+  run_rank_simta<T>(P, blockIdx.x, gridDim.x, S);
+}
+
 // All ranks of a collective in one launch on one device (tests, profiling).
 // Blocks of different ranks wait on one another, so they must be co-resident:
 // launched cooperatively.
@@ -30,6 +36,18 @@ __global__ void __launch_bounds__(512, 1) sar_emul_simt_kernel(const SarLaunchPa
   __syncthreads();
   if (!(P.participants >> P.rank & 1)) return;
   run_rank_simt<T>(P, blockIdx.x % blocks_per_rank, blocks_per_rank);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(simta::kThreads, 1) sar_emul_simta_kernel(const SarLaunchParams* params, int blocks_per_rank) {
+  __shared__ SarLaunchParams P;
+  __shared__ simta::Shared S;
+  const int r = blockIdx.x / blocks_per_rank;
+  for (uint32_t i = threadIdx.x; i < sizeof(SarLaunchParams) / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(&P)[i] = reinterpret_cast<const uint32_t*>(params + r)[i];
+  __syncthreads();
+  if (!(P.participants >> P.rank & 1)) return;
+  run_rank_simta<T>(P, blockIdx.x % blocks_per_rank, blocks_per_rank, S);
 }
 
 template <typename T>
@@ -216,6 +234,8 @@ int sar_cuda_launch(const SarLaunchParams* p, int path, int blocks, int threads,
       int e = allow_smem(sar_exec_tma_kernel<T>, sizeof(tma::Shared));
       if (e) return e;
       sar_exec_tma_kernel<T><<<blocks, tma::kThreads, sizeof(tma::Shared), st>>>(*p);
+    } else if (path == SAR_PATH_SIMTA) {
+      sar_exec_simta_kernel<T><<<blocks, simta::kThreads, 0, st>>>(*p);
     } else {
       if (threads <= 0) threads = 512;
       sar_exec_simt_kernel<T><<<blocks, threads, 0, st>>>(*p);
@@ -233,6 +253,8 @@ int sar_cuda_max_emulated_blocks(int dtype, int path, int threads) {
       allow_smem(sar_emul_tma_kernel<T>, sizeof(tma::Shared));
       return (int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sar_emul_tma_kernel<T>, tma::kThreads, sizeof(tma::Shared));
     }
+    if (path == SAR_PATH_SIMTA)
+      return (int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sar_emul_simta_kernel<T>, simta::kThreads, 0);
     return (int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sar_emul_simt_kernel<T>, threads <= 0 ? 512 : threads, 0);
   });
   return sms * per_sm;
@@ -251,6 +273,8 @@ int sar_cuda_launch_emulated(const SarLaunchParams* d_params, int n, int dtype, 
       return (int)cudaLaunchCooperativeKernel((void*)sar_emul_tma_kernel<T>, dim3(n * blocks_per_rank), dim3(tma::kThreads),
                                               args, sizeof(tma::Shared), st);
     }
+    if (path == SAR_PATH_SIMTA)
+      return (int)cudaLaunchCooperativeKernel((void*)sar_emul_simta_kernel<T>, dim3(n * blocks_per_rank), dim3(simta::kThreads), args, 0, st);
     if (threads <= 0) threads = 512;
     return (int)cudaLaunchCooperativeKernel((void*)sar_emul_simt_kernel<T>, dim3(n * blocks_per_rank), dim3(threads), args, 0, st);
   });

@@ -388,14 +388,14 @@ __device__ __forceinline__ char* mc_view_for(const SarLaunchParams& P, const Sar
 }
 
 // ------------------------------------------------------------------- simt path
+// `tid` of `nth` threads work on the tile together.
 template <typename T, int UNROLL>
-__device__ void simt_tile(const SarLaunchParams& P, const Item& it) {
+__device__ void simt_tile(const SarLaunchParams& P, const Item& it, const uint32_t tid, const uint32_t nth) {
   constexpr int N = Vec<T>::N;
   const SarOp* op = it.op;
   const uint32_t nvec = it.nelem / N;
   const uint64_t byte0 = it.elem0 * sizeof(T);
   char* own = (char*)P.comm.buf[P.rank] + byte0;
-  const uint32_t tid = threadIdx.x, nth = blockDim.x;
   char* mcv = mc_view_for(P, op);
   if (mcv) {
     mcv += byte0;
@@ -617,7 +617,7 @@ __device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t
     __syncthreads();
     if (s_state != 1) break;
     const Item it = s_item;
-    simt_tile<T, 4>(P, it);
+    simt_tile<T, 4>(P, it, threadIdx.x, blockDim.x);
     __syncthreads();   // every store of the tile is issued; s_item may be rewritten
     if (threadIdx.x == 0) {
       fence_sys();
@@ -968,6 +968,136 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       if (issued <= s) continue;
       const uint32_t use = (issued - 1 - s) / kStages;   // newest use of stage s
       while (!mbar_try_wait(&S.full[s], use & 1) && globaltimer() < limit) {}
+    }
+  }
+  __syncthreads();
+  if (tid == 0) leave_collective(P, w, nblocks);
+}
+
+// ------------------------------------------------------- simt path, decoupled
+// The simt data path with the control work taken off the threads that move data (512 threads):
+//   warps 0-13           workers: move the tile with 16-byte loads and stores (simt_tile);
+//   warp 14, one thread  control: walks the items and waits for their operands (flags in
+//                        peer memory) one item ahead of the workers;
+//   warp 15, one thread  signal: announces finished items (system-scope fence + flag stores).
+// In run_rank_simt every tile pays, on all 512 threads, the flag wait before it and the fence
+// after it; here both overlap the workers' copying.  This is also the path on which
+// reductions over, and pushes to, a whole multicast group go through the switch.
+namespace simta {
+constexpr int kThreads = 512;
+constexpr int kWorkerWarps = 14;
+constexpr int kWorkers = 32 * kWorkerWarps;
+constexpr int kSlots = 2;
+constexpr int kPendRing = 16;
+
+struct Shared {
+  TableGeom geom;
+  Item slot[kSlots];
+  int state[kSlots];          // 1: item ready, 0: table exhausted, -1: a wait failed
+  int decision;               // the state the workers act on (written by worker thread 0)
+  alignas(8) uint64_t full[kSlots];
+  alignas(8) uint64_t empty[kSlots];
+  tma::PendEntry pend[kPendRing];
+  uint32_t pend_tail;         // written by worker thread 0
+  uint32_t pend_head;         // written by the signal thread
+  uint32_t workers_done;
+};
+__device__ __forceinline__ void worker_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
+}  // namespace simta
+
+template <typename T>
+__device__ void run_rank_simta(const SarLaunchParams& P, uint32_t block, uint32_t nblocks, simta::Shared& S) {
+  using namespace simta;
+  using tma::ld_acquire_cta;
+  using tma::mbar_arrive;
+  using tma::mbar_init;
+  using tma::mbar_wait;
+  using tma::st_release_cta;
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5, lane = tid & 31;
+  WaitCtx w = enter_collective(P, block);
+  if (tid == 0) {
+    for (int s = 0; s < kSlots; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    S.pend_tail = 0; S.pend_head = 0; S.workers_done = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  resolve_table(P, S.geom, nblocks);   // ends with a block barrier
+
+  if (warp < (uint32_t)kWorkerWarps) {
+    // ----------------------------------------------------------------- workers
+    uint32_t pend_tail = 0;            // private copy of worker thread 0
+    for (uint32_t seq = 0;; ++seq) {
+      const uint32_t s = seq % kSlots;
+      // One thread waits for the control thread and decides for all workers, so that they
+      // leave the loop together even when a wait runs out for some and not for others.
+      if (tid == 0) {
+        const bool ok = mbar_wait(&S.full[s], (seq / kSlots) & 1, w);
+        *(volatile int*)&S.decision = ok ? *(volatile int*)&S.state[s] : -1;
+      }
+      worker_bar();
+      if (*(volatile int*)&S.decision != 1) break;
+      const Item it = S.slot[s];
+      simt_tile<T, 4>(P, it, tid, kWorkers);
+      worker_bar();                    // every store of the tile is issued; every worker has read the slot and the decision
+      if (tid == 0) {
+        // hand the item to the signal thread (bounded wait if its ring is full), free the slot
+        while (pend_tail - ld_acquire_cta(&S.pend_head) >= (uint32_t)kPendRing) {
+          if (*(volatile uint32_t*)w.abort_flag || globaltimer() > w.deadline) break;
+        }
+        tma::PendEntry& e = S.pend[pend_tail % kPendRing];
+        e.op = it.op; e.fidx = it.fidx; e.seq = seq;
+        ++pend_tail;
+        st_release_cta(&S.pend_tail, pend_tail);
+        mbar_arrive(&S.empty[s]);
+      }
+    }
+    if (tid == 0) st_release_cta(&S.workers_done, 1u);
+  } else if (warp == (uint32_t)kWorkerWarps) {
+    // ----------------------------------------------------------------- control
+    if (lane == 0) {
+      ItemWalker walk;
+      walk.init(&P, &S.geom, block, nblocks);
+      uint32_t arrived = 1u << P.rank;
+      for (uint32_t seq = 0;; ++seq) {
+        const uint32_t s = seq % kSlots;
+        // the slot is free once the workers are done with the item that used it last
+        if (seq >= (uint32_t)kSlots && !mbar_wait(&S.empty[s], ((seq / kSlots) - 1) & 1, w)) {
+          // the workers have stopped or the deadline has passed; they see the abort word themselves
+          break;
+        }
+        Item it;
+        int state = 1;
+        if (!walk.next(&it)) state = 0;
+        else {
+          const uint64_t t_begin = P.trace_rounds ? globaltimer() : 0;
+          if (!wait_item_ready(P, it, w, &arrived)) state = -1;
+          else if (P.trace_rounds) trace_item_start(P, it.op, t_begin, globaltimer());
+        }
+        if (state == 1) S.slot[s] = it;
+        *(volatile int*)&S.state[s] = state;
+        mbar_arrive(&S.full[s]);       // release: the workers' wait acquires the slot contents
+        if (state != 1) break;
+      }
+    }
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ signal
+    uint32_t head = 0;
+    while (true) {
+      const uint32_t done = ld_acquire_cta(&S.workers_done);
+      const uint32_t tail = ld_acquire_cta(&S.pend_tail);
+      if (head != tail) {
+        fence_sys();                   // the tiles' stores (ordered before the hand-off) become visible first
+        for (; head != tail; ++head) {
+          const tma::PendEntry& e = S.pend[head % kPendRing];
+          publish_item(P, e.op, e.fidx);
+          trace_item_end(P, e.op);
+        }
+        st_release_cta(&S.pend_head, head);
+        continue;
+      }
+      if (done) break;
+      if (globaltimer() > w.deadline + 1000000000ull) break;   // the other roles have given up long ago
+      __nanosleep(64);
     }
   }
   __syncthreads();

@@ -12,7 +12,9 @@ struct SarLaunchParams;
 extern "C" {
 #endif
 
-enum SarPath { SAR_PATH_SIMT = 0, SAR_PATH_TMA = 1 };
+// simt: every thread moves vectors and takes part in the control flow; tma: bulk-copy pipeline;
+// simta: the simt data path with control and signalling in threads of their own
+enum SarPath { SAR_PATH_SIMT = 0, SAR_PATH_TMA = 1, SAR_PATH_SIMTA = 2 };
 
 // blocks <= 0 picks the default for the path.  threads is used by the simt
 // path only (<= 0: 512).

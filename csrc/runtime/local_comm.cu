@@ -189,7 +189,7 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
   // instructions are issued by threads, not by the bulk-copy engine)
   size_t mc_off = 0;
   const sar::SymmAlloc* mc_alloc = nullptr;
-  if (!c->emulate && path == SAR_PATH_SIMT && !c->allocs.empty()) {
+  if (!c->emulate && path != SAR_PATH_TMA && !c->allocs.empty()) {
     mc_alloc = find_alloc(c, bufs, (size_t)count * esize, &mc_off);
     if (mc_alloc && !mc_alloc->mc_handle[0]) mc_alloc = nullptr;
   }

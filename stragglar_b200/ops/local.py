@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libsar_cuda.so")
 _lib = None
 
-PATHS = {"simt": 0, "tma": 1}
+PATHS = {"simt": 0, "tma": 1, "simta": 2}
 
 
 class RunOpts(C.Structure):

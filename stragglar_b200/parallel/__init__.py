@@ -29,7 +29,7 @@ def _ext():
 
 def configure(**options) -> None:
     """Options of process groups created afterwards: alg, straggler, path
-    ('tma' | 'simt'), blocks, threads, tile_bytes, timeout_s, arena_bytes,
+    ('tma' | 'simt' | 'simta'), blocks, threads, tile_bytes, timeout_s, arena_bytes,
     staging_bytes, schedule_text."""
     _options.update(options)
 

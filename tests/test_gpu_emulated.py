@@ -1,12 +1,18 @@
 """The CUDA table executor with all ranks emulated on one device (a single
 cooperative launch), against a plain PyTorch fp32/fp64 reference.  Both data
 paths (simt loads/stores and the bulk-copy pipeline) run the same tables."""
+import os
+
 import pytest
 import torch
 
 from stragglar_b200 import compiler as sc
 
 pytestmark = pytest.mark.gpu
+
+# "simta" (the simt data path with control and signalling in threads of their own) joins the matrix with
+# STRAGGLAR_TEST_SIMTA=1 until it has been exercised on a GPU
+PATHS = ["simt", "tma"] + (["simta"] if os.environ.get("STRAGGLAR_TEST_SIMTA", "0") == "1" else [])
 
 
 def _inputs(n, count, dtype, dev="cuda:0"):
@@ -52,7 +58,7 @@ TOL = {torch.float32: dict(atol=1e-5, rtol=1e-6), torch.bfloat16: dict(atol=6e-2
        torch.float16: dict(atol=8e-3, rtol=4e-3)}
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("alg", ["stragglar", "stragglar_a2a", "ring", "rhd", "direct", "rsag"])
 def test_algorithms_n8(alg, path):
     xs, want = _run(alg, 8, 40_003, path=path)
@@ -60,7 +66,7 @@ def test_algorithms_n8(alg, path):
         torch.testing.assert_close(x.double(), want, **TOL[torch.float32])
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("n", [1, 2, 4, 6])
 def test_stragglar_other_sizes(n, path):
     xs, want = _run("stragglar", n, 20_001, path=path, scale=0.5)
@@ -68,7 +74,7 @@ def test_stragglar_other_sizes(n, path):
         torch.testing.assert_close(x.double(), want, **TOL[torch.float32])
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_half_precisions(dtype, path):
     xs, want = _run("stragglar", 8, 30_005, dtype=dtype, path=path)
@@ -79,7 +85,7 @@ def test_half_precisions(dtype, path):
         assert torch.equal(x, xs[0])
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("alg", ["stragglar", "stragglar_a2a", "direct"])
 def test_prephase_done_mode(alg, path):
     xs, want = _run(alg, 8, 25_000, path=path, prephase=False)
@@ -87,7 +93,7 @@ def test_prephase_done_mode(alg, path):
         torch.testing.assert_close(x.double(), want, atol=2e-5, rtol=1e-6)
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 def test_late_straggler_swapped_to_last_rank(path):
     # physical rank 2 is 3 ms late and plays logical rank n-1
     delay = [0.0] * 8
@@ -97,7 +103,7 @@ def test_late_straggler_swapped_to_last_rank(path):
         torch.testing.assert_close(x.double(), want, **TOL[torch.float32])
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("count", [1, 5, 17, 4099])
 def test_small_and_ragged(count, path):
     xs, want = _run("stragglar", 4, count, path=path, tile_bytes=2048)
@@ -105,7 +111,7 @@ def test_small_and_ragged(count, path):
         torch.testing.assert_close(x.double(), want, **TOL[torch.float32])
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 def test_back_to_back_collectives_reuse_flags(path):
     from stragglar_b200 import ops
     n, count = 4, 100_000
@@ -120,7 +126,7 @@ def test_back_to_back_collectives_reuse_flags(path):
     comm.close()
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 def test_larger_than_l2(path):
     # 8 ranks x 64 MiB: every tile crosses HBM
     from stragglar_b200 import ops
@@ -177,7 +183,7 @@ def test_helper_kernels():
     assert 4.9 <= t0.elapsed_time(t1) < 7.0
 
 
-@pytest.mark.parametrize("path", ["simt", "tma"])
+@pytest.mark.parametrize("path", PATHS)
 def test_round_trace(path):
     """Per-round statistics: every round of a rank's table shows up, starts before it ends, rounds end in order
     on the straggler (its matchings are serial), and a run without tracing leaves the record untouched."""
