@@ -377,6 +377,10 @@ void ProcessGroupStragglar::allreduce_impl(Side& s, at::Tensor& tensor, float sc
   }
 }
 
+// what the table kernels reduce themselves; everything else takes allreduce_generic
+static bool table_dtype(at::ScalarType t) { return t == at::kFloat || t == at::kBFloat16 || t == at::kHalf; }
+static bool table_op(const c10d::ReduceOp& op) { return op == c10d::ReduceOp::SUM || op == c10d::ReduceOp::AVG; }
+
 static float scale_for(const c10d::ReduceOp& op, int n) {
   if (op == c10d::ReduceOp::SUM) return 1.0f;
   if (op == c10d::ReduceOp::AVG) return 1.0f / (float)n;
@@ -390,7 +394,10 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allreduce(std::vector<at::
   std::lock_guard<std::mutex> lk(mu_);
   Side& s = side(tensors[0]);
   auto w = begin(s, c10d::OpType::ALLREDUCE, tensors);
-  allreduce_impl(s, tensors[0], scale_for(opts.reduceOp, getSize()), std::nullopt);
+  if (table_dtype(tensors[0].scalar_type()) && table_op(opts.reduceOp))
+    allreduce_impl(s, tensors[0], scale_for(opts.reduceOp, getSize()), std::nullopt);
+  else
+    allreduce_generic(s, tensors[0], opts.reduceOp);
   finish(s, w);
   return w;
 }
@@ -411,7 +418,11 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allreduce_coalesced(std::v
   std::lock_guard<std::mutex> lk(mu_);
   Side& s = side(tensors[0]);
   auto w = begin(s, c10d::OpType::ALLREDUCE_COALESCED, tensors);
-  for (auto& t : tensors) { check_contiguous(t); allreduce_impl(s, t, scale_for(opts.reduceOp, getSize()), std::nullopt); }
+  for (auto& t : tensors) {
+    check_contiguous(t);
+    if (table_dtype(t.scalar_type()) && table_op(opts.reduceOp)) allreduce_impl(s, t, scale_for(opts.reduceOp, getSize()), std::nullopt);
+    else allreduce_generic(s, t, opts.reduceOp);
+  }
   finish(s, w);
   return w;
 }
@@ -422,6 +433,15 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::reduce(std::vector<at::Ten
   std::lock_guard<std::mutex> lk(mu_);
   Side& s = side(tensors[0]);
   auto w = begin(s, c10d::OpType::REDUCE, tensors);
+  if (!(table_dtype(tensors[0].scalar_type()) && table_op(opts.reduceOp))) {
+    // the gather-based path reduces on every rank; only the root keeps the result
+    std::optional<c10::cuda::CUDAStreamGuard> guard;
+    if (s.t->cuda()) guard.emplace(*s.stream);     // the scratch copy is made (and lives) on the communication stream
+    at::Tensor x = getRank() == opts.rootRank ? tensors[0] : tensors[0].clone();
+    allreduce_generic(s, x, opts.reduceOp);
+    finish(s, w);
+    return w;
+  }
   // everybody computes the sum on a staged copy; only the root keeps it
   Transport& t = *s.t;
   at::Tensor& x = tensors[0];
@@ -470,20 +490,63 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::_allgather_base(at::Tensor
   std::lock_guard<std::mutex> lk(mu_);
   Side& s = side(input);
   auto w = begin(s, c10d::OpType::_ALLGATHER_BASE, {output});
+  gather_all(s, output.data_ptr(), input.data_ptr(), input.nbytes());
+  finish(s, w);
+  return w;
+}
+
+// out[r * bytes ...] = rank r's `in`, on every rank, through the staging area
+void ProcessGroupStragglar::gather_all(Side& s, void* out, const void* in, size_t bytes) {
   Transport& t = *s.t;
-  const size_t bytes = input.nbytes(), piece = t.staging_bytes();
+  const int n = getSize();
+  const size_t piece = t.staging_bytes();
   for (size_t off = 0; off < bytes || (bytes == 0 && off == 0); off += piece) {
     const size_t k = std::min(piece, bytes - off);
-    copy_local(s, t.data(getRank()) + t.staging_off(), (char*)input.data_ptr() + off, k);
+    copy_local(s, t.data(getRank()) + t.staging_off(), (const char*)in + off, k);
     device_barrier(s);
     std::vector<std::tuple<int, size_t, void*, size_t>> segs;
-    for (int r = 0; r < n; ++r) segs.push_back({r, t.staging_off(), (char*)output.data_ptr() + (size_t)r * bytes + off, k});
+    for (int r = 0; r < n; ++r) segs.push_back({r, t.staging_off(), (char*)out + (size_t)r * bytes + off, k});
     pull(s, segs);
     device_barrier(s);
     if (bytes == 0) break;
   }
-  finish(s, w);
-  return w;
+}
+
+// What the table kernels do not cover -- integer, fp64 and bool tensors, MIN / MAX / PRODUCT and
+// the bitwise operations: every rank gathers all contributions and reduces them itself with
+// ATen, on the communication stream.  Meant for the small control tensors frameworks
+// all-reduce besides the gradients (DDP's bitmap of unused parameters, found-inf flags,
+// counters); the bytes on the wire are world_size times those of a real all-reduce.
+
+void ProcessGroupStragglar::allreduce_generic(Side& s, at::Tensor& tensor, const c10d::ReduceOp& op) {
+  const int n = getSize();
+  const int64_t numel = tensor.numel();
+  if (numel == 0) return;
+  std::optional<c10::cuda::CUDAStreamGuard> guard;
+  if (s.t->cuda()) guard.emplace(*s.stream);      // allocation and the ATen kernels below on the communication stream
+  at::Tensor all = at::empty({(int64_t)n, numel}, tensor.options());
+  gather_all(s, all.data_ptr(), tensor.data_ptr(), tensor.nbytes());
+  at::Tensor flat = tensor.view({-1});
+  at::Tensor r;
+  if (op == c10d::ReduceOp::SUM) r = all.sum(0, false, tensor.scalar_type());
+  else if (op == c10d::ReduceOp::AVG) {
+    TORCH_CHECK(at::isFloatingType(tensor.scalar_type()), "ReduceOp.AVG needs a floating-point tensor");
+    r = all.sum(0) / (double)n;
+  } else if (op == c10d::ReduceOp::MIN) r = all.amin(0);
+  else if (op == c10d::ReduceOp::MAX) r = all.amax(0);
+  else if (op == c10d::ReduceOp::PRODUCT) r = all.prod(0, false, tensor.scalar_type());
+  else if (op == c10d::ReduceOp::BAND || op == c10d::ReduceOp::BOR || op == c10d::ReduceOp::BXOR) {
+    TORCH_CHECK(at::isIntegralType(tensor.scalar_type(), /*includeBool=*/true), "bitwise reductions need an integer tensor");
+    r = all[0].clone();
+    for (int k = 1; k < n; ++k) {
+      if (op == c10d::ReduceOp::BAND) r.bitwise_and_(all[k]);
+      else if (op == c10d::ReduceOp::BOR) r.bitwise_or_(all[k]);
+      else r.bitwise_xor_(all[k]);
+    }
+  } else {
+    TORCH_CHECK(false, "stragglar backend: unsupported ReduceOp");
+  }
+  flat.copy_(r.to(tensor.scalar_type()));
 }
 
 c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allgather(std::vector<std::vector<at::Tensor>>& outputs, std::vector<at::Tensor>& inputs, const c10d::AllgatherOptions& opts) {

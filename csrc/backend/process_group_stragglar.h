@@ -153,6 +153,8 @@ class ProcessGroupStragglar : public c10d::Backend {
   void copy_local(Side& s, void* dst, const void* src, size_t bytes);
   void pull(Side& s, const std::vector<std::tuple<int, size_t, void*, size_t>>& segs);  // (peer, offset in data region, dst, bytes)
   void allreduce_impl(Side& s, at::Tensor& t, float scale, std::optional<at::ScalarType> comm_dtype);
+  void allreduce_generic(Side& s, at::Tensor& t, const c10d::ReduceOp& op);   // any dtype / op: gather + local reduce
+  void gather_all(Side& s, void* out, const void* in, size_t bytes);
 
   c10::intrusive_ptr<c10d::Store> store_;
   BackendOptions opts_;

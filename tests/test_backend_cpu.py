@@ -368,3 +368,82 @@ def _auto(rank, world):
 
 def test_auto_algorithm_selection():
     run_ranks(4, _auto)
+
+
+def _other_dtypes_and_ops(rank, world):
+    # integer / fp64 / bool tensors and MIN, MAX, PRODUCT, bitwise ops take the gather-and-reduce path
+    x = torch.arange(10, dtype=torch.int64) * (rank + 1)
+    dist.all_reduce(x)
+    assert torch.equal(x, torch.arange(10, dtype=torch.int64) * sum(range(1, world + 1)))
+    y = torch.full((7,), float(rank), dtype=torch.float64)
+    dist.all_reduce(y, op=dist.ReduceOp.MAX)
+    assert torch.equal(y, torch.full((7,), float(world - 1), dtype=torch.float64))
+    z = _seeded(rank, 300)
+    dist.all_reduce(z, op=dist.ReduceOp.MIN)
+    assert torch.equal(z, torch.stack([_seeded(r, 300) for r in range(world)]).amin(0))
+    p = torch.full((5,), 2.0)
+    dist.all_reduce(p, op=dist.ReduceOp.PRODUCT)
+    assert torch.equal(p, torch.full((5,), 2.0 ** world))
+    bits = torch.tensor([1 << rank, 0xff, rank], dtype=torch.int32)
+    b_or, b_and, b_xor = bits.clone(), bits.clone(), bits.clone()
+    dist.all_reduce(b_or, op=dist.ReduceOp.BOR)
+    dist.all_reduce(b_and, op=dist.ReduceOp.BAND)
+    dist.all_reduce(b_xor, op=dist.ReduceOp.BXOR)
+    ranks = list(range(world))
+    import functools
+    import operator
+    assert b_or.tolist() == [(1 << world) - 1, 0xff, functools.reduce(operator.or_, ranks)]
+    assert b_and.tolist() == [0, 0xff, functools.reduce(operator.and_, ranks)]
+    assert b_xor.tolist() == [(1 << world) - 1, 0xff if world % 2 else 0, functools.reduce(operator.xor, ranks)]
+    flag = torch.tensor([rank == 1])
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    assert flag.item() is True
+    m = torch.full((4,), rank + 1, dtype=torch.int32)
+    dist.all_reduce(m, op=dist.ReduceOp.SUM)           # several in a row reuse the staging area safely
+    dist.all_reduce(m, op=dist.ReduceOp.MAX)
+    assert m.tolist() == [sum(range(1, world + 1))] * 4
+    with pytest.raises(RuntimeError, match="floating-point"):
+        dist.all_reduce(torch.ones(3, dtype=torch.int32), op=dist.ReduceOp.AVG)
+    # reduce to a root: only the root's tensor changes
+    t = torch.full((6,), rank + 1, dtype=torch.int64)
+    dist.reduce(t, dst=1, op=dist.ReduceOp.MAX)
+    assert t.tolist() == [world if rank == 1 else rank + 1] * 6
+
+
+def test_integer_tensors_and_other_reduce_ops():
+    run_ranks(4, _other_dtypes_and_ops)
+
+
+def _ddp_unused(rank, world):
+    # find_unused_parameters=True makes DDP all-reduce an int32 bitmap next to the gradients
+    torch.manual_seed(0)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b, self.c = torch.nn.Linear(6, 6), torch.nn.Linear(6, 3), torch.nn.Linear(6, 3)
+        def forward(self, x, use_c):
+            h = torch.tanh(self.a(x))
+            return self.c(h) if use_c else self.b(h)
+
+    net = Net()
+    ddp = torch.nn.parallel.DistributedDataParallel(net, find_unused_parameters=True)
+    x = torch.randn(5, 6, generator=torch.Generator().manual_seed(20 + rank))
+    ddp(x, False).sum().backward()
+    ref = Net()
+    ref.load_state_dict(net.state_dict())
+    grads = []
+    for r in range(world):
+        ref.zero_grad()
+        ref(torch.randn(5, 6, generator=torch.Generator().manual_seed(20 + r)), False).sum().backward()
+        grads.append([p.grad.clone() if p.grad is not None else None for p in ref.parameters()])
+    for i, p in enumerate(net.parameters()):
+        want = [g[i] for g in grads]
+        if want[0] is None:
+            assert p.grad is None or torch.count_nonzero(p.grad) == 0
+        else:
+            torch.testing.assert_close(p.grad, torch.stack(want).mean(0), atol=1e-6, rtol=1e-5)
+
+
+def test_ddp_with_unused_parameters():
+    run_ranks(2, _ddp_unused)
