@@ -285,6 +285,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.epoch_base = epoch; P.scale = scale; P.dtype = dt;
       P.timeout_ns = (uint64_t)(opts_.timeout_s * 1e9);
       P.status = t.status(); P.trace = reinterpret_cast<uint64_t*>(t.status() + 4); P.delay_ns = 0;
+      P.gate_rounds = (c.gate_rounds && count * esize >= sar::gate_min_bytes()) ? 1u : 0u;
       SAR_CUDA_CHECK(sar_cuda_launch(&P, opts_.path, blocks, opts_.threads, s.stream->stream()));
       ++launches_;
     } else {
@@ -298,6 +299,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       sar::HostLaunch l;
       l.geom = g; l.dtype = (SarDtype)dt; l.scale = scale; l.epoch_base = epoch; l.timeout_s = opts_.timeout_s;
       l.participants = c.participants;
+      l.gate_rounds = c.gate_rounds && count * esize >= sar::gate_min_bytes();
       const uint32_t st = sar::host_run_block(v, rt, l, 0, 1);
       if (st != SAR_OK) {
         as_atomic(&t.ctrl(me, c.channel)->abort_flag)->store(0);

@@ -29,6 +29,8 @@ void sar_program_free(sar_program* p);
 int sar_program_num_phases(const sar_program* p);
 const sar_table* sar_program_phase(const sar_program* p, int i);
 int sar_table_channel(const sar_table* t);
+int sar_table_gate_rounds(const sar_table* t);   // 1: launch with round gating (for buffers of sar_gate_min_bytes() or more)
+uint64_t sar_gate_min_bytes(void);
 int sar_table_blocks_hint(const sar_table* t);   // 0, or the largest block count per rank worth using
 uint32_t sar_table_participants(const sar_table* t);
 int sar_table_nranks(const sar_table* t);

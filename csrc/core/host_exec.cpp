@@ -2,6 +2,7 @@
 
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <thread>
@@ -50,6 +51,11 @@ static inline float load_elem(const void* p, uint64_t i, SarDtype d) {
 static inline void store_elem(void* p, uint64_t i, SarDtype d, float v) {
   if (d == SAR_F32) ((float*)p)[i] = v;
   else ((uint16_t*)p)[i] = d == SAR_BF16 ? f_to_bf16(v) : f_to_f16(v);
+}
+
+uint64_t gate_min_bytes() {
+  const char* v = getenv("STRAGGLAR_GATE_MIN_BYTES");
+  return (v && *v) ? strtoull(v, nullptr, 10) : (48ull << 20);
 }
 
 uint32_t pick_tile_elems(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t blocks, uint32_t min_bytes,
@@ -102,7 +108,8 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   const int me = v.rank;
   SarCtrl* my_ctrl_raw = reinterpret_cast<SarCtrl*>(v.ctrl[me]);
   (void)my_ctrl_raw;
-  auto ctrl_word = [&](int r, int idx) { return v.ctrl[r] + idx; };  // 0 arrival, 1 exited, 2 abort, 3 blocks_done
+  // 0 arrival, 1 exited, 2 abort, 3 blocks_done, 4 rounds_done, 5 round_count (the words of SarCtrl)
+  auto ctrl_word = [&](int r, int idx) { return v.ctrl[r] + idx; };
   Waiter w{clk::now() + std::chrono::duration_cast<clk::duration>(std::chrono::duration<double>(l.timeout_s + l.delay_ms * 1e-3)),
            ctrl_word(me, 2)};
   uint32_t status = SAR_OK;
@@ -120,6 +127,19 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   };
 
   const size_t nrounds = t.round_begin.empty() ? 0 : t.round_begin.size() - 1;
+  // round gating: items this rank has in every schedule round (all lanes); the table's round
+  // list is compact, so the schedule round is taken from the ops
+  uint32_t round_items[SAR_GATE_ALL_DONE + 1] = {};
+  if (l.gate_rounds)
+    for (const SarOp& op : t.ops)
+      if (op.round < SAR_GATE_ALL_DONE) round_items[op.round] += sar_op_tiles(g, op);
+  auto next_round_with_items = [&](uint32_t from) -> uint32_t {
+    for (uint32_t rd = from; rd < SAR_GATE_ALL_DONE; ++rd) if (round_items[rd]) return rd;
+    return SAR_GATE_ALL_DONE;
+  };
+  if (l.gate_rounds && block == 0)
+    ctrl_word(me, 4)->store(l.epoch_base + next_round_with_items(0), std::memory_order_release);
+  uint32_t gate_passed = 0;   // schedule rounds up to this one may start
   uint32_t table_lanes = 1;
   for (const SarOp& op : t.ops) if (op.lane) table_lanes = 2;
   uint32_t lanes, lane, lblock, lnblocks;
@@ -150,8 +170,15 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
       if (local_tile >= t1 - t0) continue;
       const uint32_t tile = t0 + local_tile;
       const uint32_t fidx = sar_flag_index(g, op.chunk, tile);
-      // wait for the operands
       bool ok = true;
+      // round gate: every participant has finished the rounds before this one
+      if (l.gate_rounds && op.round > gate_passed) {
+        for (int r = 0; r < v.nranks && ok; ++r)
+          if ((l.participants >> r & 1) && !w.wait(ctrl_word(r, 4), l.epoch_base + op.round)) { give_up(SAR_TIMEOUT_FLAG); ok = false; }
+        if (!ok) break;
+        gate_passed = op.round;
+      }
+      // wait for the operands
       for (int q = 0; q < op.nsrc && ok; ++q) {
         const int src = op.src[q];
         if (!need_arrival(src)) { ok = false; break; }
@@ -187,6 +214,11 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
       if (op.kind == SAR_PUSH)
         for (int q = 0; q < op.nsrc; ++q)
           v.flags[op.src[q]][fidx].store(l.epoch_base + op.push_ver, std::memory_order_release);
+      // round gate: whoever finishes the rank's last item of the round announces the next round
+      if (l.gate_rounds && ctrl_word(me, 5)->fetch_add(1, std::memory_order_acq_rel) + 1 == round_items[op.round]) {
+        ctrl_word(me, 5)->store(0, std::memory_order_relaxed);
+        ctrl_word(me, 4)->store(l.epoch_base + next_round_with_items(op.round + 1u), std::memory_order_release);
+      }
     }
     item_base += items;
   }
@@ -195,6 +227,7 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   uint32_t done = ctrl_word(me, 3)->fetch_add(1, std::memory_order_acq_rel) + 1;
   if (done == (uint32_t)nblocks_all) {
     ctrl_word(me, 3)->store(0, std::memory_order_relaxed);
+    ctrl_word(me, 5)->store(0, std::memory_order_relaxed);   // a run that gave up may have left a partial count
     if (status == SAR_OK && !ctrl_word(me, 2)->load(std::memory_order_relaxed)) {
       ctrl_word(me, 1)->store(l.epoch_base, std::memory_order_release);
       for (int r = 0; r < v.nranks; ++r)
@@ -258,6 +291,7 @@ static uint32_t run_phases(const std::vector<const Compiled*>& phases, void* con
               uint32_t te = tile_elems ? tile_elems : pick_tile_elems(count, esize, c.num_chunks, blocks, 256, 1 << 16);
               l.geom = make_geom(count, esize, c.num_chunks, te);
               l.dtype = dtype; l.scale = scale; l.timeout_s = timeout_s; l.participants = c.participants;
+              l.gate_rounds = c.gate_rounds;
               l.epoch_base = (uint32_t)(rep + 1) * SAR_VER_STRIDE;
               l.delay_ms = (!delayed && delay_ms) ? delay_ms[r] : 0.0;
               delayed = true;

@@ -30,6 +30,7 @@ struct HostLaunch {
   double timeout_s = 10.0;
   double delay_ms = 0.0;                  // sleep before arriving (an injected straggler delay)
   uint32_t participants = 0;              // ranks that run this collective (exit barrier set)
+  bool gate_rounds = false;               // rounds one after the other (every rank of the launch must agree)
 };
 
 // Executes block `block` of `nblocks` of this rank's table.  Every block of
@@ -44,6 +45,12 @@ uint32_t host_execute(const Compiled& c, void* const* bufs, uint64_t count, SarD
 // A whole program (one or two phases), every rank's phases in stream order.
 uint32_t host_execute_program(const Program& p, void* const* bufs, uint64_t count, SarDtype dtype, uint32_t tile_elems,
                               float scale, int blocks, const double* delay_ms, double timeout_s);
+
+// Round gating costs a hand-shake per round and pays once a round's chunk takes much longer than that on
+// the link: a gated table is launched with gating for buffers of at least this many bytes
+// (STRAGGLAR_GATE_MIN_BYTES, default 48 MiB: in the tile-level model of an 8-GPU box the gated rounds win
+// from 64 MiB up and lose at 32 MiB).  Every rank of a launch sees the same size, hence the same answer.
+uint64_t gate_min_bytes();
 
 uint32_t pick_tile_elems(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t blocks, uint32_t min_bytes,
                          uint32_t max_bytes);

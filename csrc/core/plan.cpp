@@ -5,6 +5,7 @@
 #include <bitset>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <sstream>
 
@@ -358,6 +359,12 @@ Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* 
   // With one or two ranks there is a single flow per link and more blocks keep helping.
   if (alg == "stragglar" && n >= 4) p.blocks_hint = 64;
   if (alg == "stragglar_a2a" && n >= 4) p.blocks_hint = 32;
+  // Round gating pays for the synthesized schedule, whose rounds are matchings (a tile-level model of
+  // the executor puts it at 0.86-0.90 of the link rate against 0.73-0.78 with free-running rounds);
+  // the other algorithms lose a little to the extra hand-shake per round.  Opt-in until measured:
+  // STRAGGLAR_GATE=1 gates "stragglar", STRAGGLAR_GATE=all every algorithm, 0 none.
+  const char* gate = getenv("STRAGGLAR_GATE");
+  if (gate && *gate) p.gate_rounds = !strcmp(gate, "all") || (atoi(gate) != 0 && alg == "stragglar" && n >= 4);
   return p;
 }
 
@@ -585,6 +592,10 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
   }
   if (out.max_version >= (int)SAR_VER_STRIDE) throw CompileError("too many versions of one slot");
   out.blocks_hint = plan.blocks_hint;
+  out.gate_rounds = plan.gate_rounds;
+  for (const RankTable& rt : out.ranks)
+    for (const SarOp& op : rt.ops)
+      if (op.round >= SAR_GATE_ALL_DONE) out.gate_rounds = false;   // does not fit the announcement word
   // result check
   const uint32_t want = full_mask(n);
   for (int r : plan.participants) {

@@ -92,8 +92,22 @@ struct SarCtrl {
   uint32_t exited;     // epoch_base of the newest collective this rank has left
   uint32_t abort_flag; // set by any block that timed out; makes the others return
   uint32_t blocks_done;// local counter to find the last block of a launch
-  uint32_t reserved[28];
+  // round gating (see SAR_GATE_ALL_DONE): epoch_base + the first schedule round this rank has not
+  // finished yet (read by peers), and a local counter of the items finished in the current round
+  uint32_t rounds_done;
+  uint32_t round_count;
+  uint32_t reserved[26];
 };
+static_assert(sizeof(SarCtrl) == 128, "SarCtrl layout");
+// Round gating.  The rounds of a matching-based schedule are contention-free one at a time: in
+// every round a rank sends at most one chunk and receives at most one.  When the rounds overlap
+// freely, a rank that holds a finished chunk serves the readers of several rounds at once, each
+// at a fraction of the link rate, and what depends on them is late.  With gating, an item of
+// round r starts only when every participant has finished its items of all rounds before r
+// (`rounds_done` >= epoch_base + r); a rank without items in a round skips it when it
+// announces.  Tiles still pipeline inside a round.  SAR_GATE_ALL_DONE is announced after the
+// last round; it bounds the number of rounds a gated table may have (< SAR_VER_STRIDE).
+#define SAR_GATE_ALL_DONE 31u
 
 // Chunk geometry for `count` elements of `esize` bytes in `num_chunks` chunks.
 // Chunks are contiguous, start on 16-byte boundaries and differ by at most one

@@ -54,6 +54,9 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // 16-byte load that is coherent at system scope (never served from a stale L1 line)
@@ -212,6 +215,7 @@ struct TableGeom {
   RoundGeom round[2][SAR_MAX_ROUNDS];   // per lane
   uint32_t num_rounds;
   uint32_t lanes;                       // lanes in effect for this launch (1 or 2)
+  uint32_t round_items[SAR_GATE_ALL_DONE + 1];   // round gating: this rank's items per schedule round (all lanes)
 };
 
 // All threads of the block; ends with a block barrier.
@@ -227,6 +231,13 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t n
     G.op[o].elem_end = cb + sar_chunk_len(P.geom, op.chunk);
     G.op[o].ntiles = t1 - t0;
     G.op[o].tile0 = t0;
+  }
+  if (threadIdx.x == 0 && P.gate_rounds) {
+    for (uint32_t r = 0; r <= SAR_GATE_ALL_DONE; ++r) G.round_items[r] = 0;
+    for (uint32_t o = 0; o < nops && o < SAR_MAX_OPS; ++o) {
+      const SarOp op = P.ops[o];
+      if (op.round < SAR_GATE_ALL_DONE) G.round_items[op.round] += sar_op_tiles(P.geom, op);
+    }
   }
   if (threadIdx.x == 0) {
     uint32_t table_lanes = 1;
@@ -317,9 +328,38 @@ __device__ __forceinline__ void trace_item_end(const SarLaunchParams& P, const S
   atomicMax((unsigned long long*)&P.trace[2 + SAR_MAX_ROUNDS + op->round], (unsigned long long)globaltimer());
 }
 
-// Waits (one thread) until every operand of the item is ready.
-__device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const WaitCtx& w, uint32_t* arrived_mask) {
+// ---- round gating (see SAR_GATE_ALL_DONE in table.h)
+__device__ __forceinline__ uint32_t next_round_with_items(const TableGeom& G, uint32_t from) {
+  for (uint32_t r = from; r < SAR_GATE_ALL_DONE; ++r) if (G.round_items[r]) return r;
+  return SAR_GATE_ALL_DONE;
+}
+// One thread of the rank's block 0, after resolve_table: the first round this rank has items in.
+__device__ __forceinline__ void gate_announce_first(const SarLaunchParams& P, const TableGeom& G) {
+  st_release_sys(&P.comm.ctrl[P.rank]->rounds_done, P.epoch_base + next_round_with_items(G, 0));
+}
+// The thread that has just announced an item: counts it, and announces the rank's next round when
+// it was the last item of the current one.  (With gating all items in flight on a rank belong to
+// one round, so one counter serves all rounds.)
+__device__ __forceinline__ void gate_item_done(const SarLaunchParams& P, const TableGeom& G, const SarOp* op) {
+  if (!P.gate_rounds || op->round >= SAR_GATE_ALL_DONE) return;
+  SarCtrl* me = P.comm.ctrl[P.rank];
+  if (atomicAdd(&me->round_count, 1u) + 1u != G.round_items[op->round]) return;
+  atomicExch(&me->round_count, 0u);
+  fence_sys();
+  st_relaxed_sys(&me->rounds_done, P.epoch_base + next_round_with_items(G, op->round + 1u));
+}
+
+// Waits (one thread) until every operand of the item is ready.  `gate_passed`: the newest schedule
+// round this thread has seen open (round gating).
+__device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const WaitCtx& w, uint32_t* arrived_mask,
+                                uint32_t* gate_passed) {
   const SarOp* op = it.op;
+  if (P.gate_rounds && op->round > *gate_passed && op->round < SAR_GATE_ALL_DONE) {
+    for (int r = 0; r < P.nranks; ++r)
+      if ((P.participants >> r & 1) && !wait_word(&P.comm.ctrl[r]->rounds_done, P.epoch_base + op->round, w, SAR_TIMEOUT_FLAG))
+        return false;
+    *gate_passed = op->round;
+  }
   for (int q = 0; q < op->nsrc; ++q) {
     const int src = op->src[q];
     if (!(*arrived_mask >> src & 1)) {
@@ -337,9 +377,6 @@ __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const 
 // Announces a finished tile.  The caller has ordered the tile's stores before
 // this call at system scope (fence_sys after the block barrier); the flags are
 // plain system-scope stores after that fence (release pattern).
-__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ void publish_item(const SarLaunchParams& P, const SarOp* op, uint32_t fidx) {
   if (op->kind != SAR_PUSH) st_relaxed_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
   if (op->kind == SAR_REDUCE_PUSH) st_relaxed_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
@@ -577,6 +614,7 @@ __device__ void leave_collective(const SarLaunchParams& P, const WaitCtx& w, uin
   const uint32_t done = atomicAdd(&me->blocks_done, 1u) + 1u;
   if (done != nblocks) return;
   me->blocks_done = 0;
+  me->round_count = 0;   // a launch that gave up may have left a partial count
   __threadfence();
   if (*(volatile uint32_t*)w.abort_flag == 0) {
     fence_sys();
@@ -599,15 +637,18 @@ __device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t
   WaitCtx w = enter_collective(P, block);
   resolve_table(P, G, nblocks);
   ItemWalker walk;
-  uint32_t arrived = 1u << P.rank;
-  if (threadIdx.x == 0) walk.init(&P, &G, block, nblocks);
+  uint32_t arrived = 1u << P.rank, gate_passed = 0;
+  if (threadIdx.x == 0) {
+    if (P.gate_rounds && block == 0) gate_announce_first(P, G);
+    walk.init(&P, &G, block, nblocks);
+  }
   while (true) {
     if (threadIdx.x == 0) {
       Item it;
       if (!walk.next(&it)) s_state = 0;
       else {
         const uint64_t t_begin = P.trace_rounds ? globaltimer() : 0;
-        if (!wait_item_ready(P, it, w, &arrived)) s_state = -1;
+        if (!wait_item_ready(P, it, w, &arrived, &gate_passed)) s_state = -1;
         else {
           if (P.trace_rounds) trace_item_start(P, it.op, t_begin, globaltimer());
           s_item = it; s_state = 1;
@@ -623,6 +664,7 @@ __device__ void run_rank_simt(const SarLaunchParams& P, uint32_t block, uint32_t
       fence_sys();
       publish_item(P, it.op, it.fidx);
       trace_item_end(P, it.op);
+      gate_item_done(P, G, it.op);
     }
   }
   __syncthreads();
@@ -761,9 +803,10 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
+      if (P.gate_rounds && block == 0) gate_announce_first(P, S.geom);
       ItemWalker walk;
       walk.init(&P, &S.geom, block, nblocks);
-      uint32_t arrived = 1u << P.rank;
+      uint32_t arrived = 1u << P.rank, gate_passed = 0;
       uint32_t seq = 0;           // pieces issued
       bool ok = true;
       Item it;
@@ -774,7 +817,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       };
       while (ok && walk.next(&it)) {
         const uint64_t t_begin = P.trace_rounds ? globaltimer() : 0;
-        if (!wait_item_ready(P, it, w, &arrived)) { ok = false; break; }
+        if (!wait_item_ready(P, it, w, &arrived, &gate_passed)) { ok = false; break; }
         if (P.trace_rounds) trace_item_start(P, it.op, t_begin, globaltimer());
         fence_proxy_async_global();   // flags were acquired through the generic proxy; the copies use the async one
         const SarOp* op = it.op;
@@ -946,6 +989,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
           const PendEntry& e = S.pend[(head + i) % kPendRing];
           publish_item(P, e.op, e.fidx);
           trace_item_end(P, e.op);
+          gate_item_done(P, S.geom, e.op);
         }
         head += n;
         st_release_cta(&S.pend_head, head);
@@ -1055,9 +1099,10 @@ __device__ void run_rank_simta(const SarLaunchParams& P, uint32_t block, uint32_
   } else if (warp == (uint32_t)kWorkerWarps) {
     // ----------------------------------------------------------------- control
     if (lane == 0) {
+      if (P.gate_rounds && block == 0) gate_announce_first(P, S.geom);
       ItemWalker walk;
       walk.init(&P, &S.geom, block, nblocks);
-      uint32_t arrived = 1u << P.rank;
+      uint32_t arrived = 1u << P.rank, gate_passed = 0;
       for (uint32_t seq = 0;; ++seq) {
         const uint32_t s = seq % kSlots;
         // the slot is free once the workers are done with the item that used it last
@@ -1070,7 +1115,7 @@ __device__ void run_rank_simta(const SarLaunchParams& P, uint32_t block, uint32_
         if (!walk.next(&it)) state = 0;
         else {
           const uint64_t t_begin = P.trace_rounds ? globaltimer() : 0;
-          if (!wait_item_ready(P, it, w, &arrived)) state = -1;
+          if (!wait_item_ready(P, it, w, &arrived, &gate_passed)) state = -1;
           else if (P.trace_rounds) trace_item_start(P, it.op, t_begin, globaltimer());
         }
         if (state == 1) S.slot[s] = it;
@@ -1091,6 +1136,7 @@ __device__ void run_rank_simta(const SarLaunchParams& P, uint32_t block, uint32_
           const tma::PendEntry& e = S.pend[head % kPendRing];
           publish_item(P, e.op, e.fidx);
           trace_item_end(P, e.op);
+          gate_item_done(P, S.geom, e.op);
         }
         st_release_cta(&S.pend_head, head);
         continue;

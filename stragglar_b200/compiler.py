@@ -73,7 +73,7 @@ def lib():
             L.sar_host_execute_program.restype = C.c_uint32
             L.sar_host_execute_program.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_uint64, C.c_int, C.c_uint32,
                                                    C.c_float, C.c_int, C.POINTER(C.c_double), C.c_double]
-            for name in ("nranks", "num_chunks", "num_rounds", "max_version", "channel", "blocks_hint"):
+            for name in ("nranks", "num_chunks", "num_rounds", "max_version", "channel", "blocks_hint", "gate_rounds"):
                 f = getattr(L, f"sar_table_{name}")
                 f.restype, f.argtypes = C.c_int, [C.c_void_p]
             for name in ("num_ops", "num_round_begin"):
@@ -121,6 +121,7 @@ class Table:
         self.max_version = L.sar_table_max_version(handle)
         self.channel = L.sar_table_channel(handle)
         self.blocks_hint = L.sar_table_blocks_hint(handle)
+        self.gate_rounds = bool(L.sar_table_gate_rounds(handle))   # rounds run one after the other (STRAGGLAR_GATE)
         self.participants = L.sar_table_participants(handle)
         self.ranks: List[RankTable] = []
         for r in range(self.n):
@@ -207,6 +208,13 @@ def pick_tile_elems(count: int, esize: int, num_chunks: int, blocks: int, min_by
     return lib().sar_pick_tile_elems(count, esize, num_chunks, blocks, min_bytes, max_bytes)
 
 
+def gate_min_bytes() -> int:
+    """Buffers of at least this many bytes run a gated table with round gating (STRAGGLAR_GATE_MIN_BYTES)."""
+    f = lib().sar_gate_min_bytes
+    f.restype = C.c_uint64
+    return int(f())
+
+
 def status_string(code: int) -> str:
     return lib().sar_status_string(code).decode()
 
@@ -251,7 +259,8 @@ def describe(program: Program) -> str:
         out.append(f"phase {pi}: channel {t.channel}, {t.num_chunks} chunks, {t.num_rounds} rounds, "
                    f"participants {[r for r in range(t.n) if t.takes_part(r)]}, "
                    f"link traffic {t.link_chunks():g} chunks per direction on the busiest rank"
-                   + (f", at most {t.blocks_hint} blocks per rank" if t.blocks_hint else ""))
+                   + (f", at most {t.blocks_hint} blocks per rank" if t.blocks_hint else "")
+                   + (", rounds gated" if t.gate_rounds else ""))
         for r in t.ranks:
             if not len(r.ops):
                 continue

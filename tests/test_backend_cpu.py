@@ -132,8 +132,9 @@ def _collectives(rank, world):
         wanth = torch.stack([_seeded(r, 2050, dt).double() for r in range(world)]).sum(0)
         dist.all_reduce(h)
         torch.testing.assert_close(h.double(), wanth, atol=tol, rtol=2e-2)
-    with pytest.raises(RuntimeError):
-        dist.all_reduce(torch.ones(4), op=dist.ReduceOp.MAX)
+    mx = torch.full((4,), float(rank))
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)          # not a table operation: gathered and reduced locally
+    assert (mx == world - 1).all()
     # coalesced forms, reached through the functional collectives (what FSDP-style code uses)
     import torch.distributed._functional_collectives as fc
     ins = [torch.arange(world * 3).float() + rank, torch.arange(world * 5).float() * 2 + rank]

@@ -216,3 +216,35 @@ def test_table_listing_cli(capsys):
     text = capsys.readouterr().out
     assert "phase 0" in text and "match" in text and "rank 3" in text
     assert sc.main(["rhd", "6"]) == 1 and "power-of-two" in capsys.readouterr().out
+
+
+def test_round_gating_attribute_and_host_execution(monkeypatch):
+    """STRAGGLAR_GATE marks tables for round gating (rounds one after the other); the host executor runs gated
+    tables of every algorithm to the same sums, with several threads per rank and a late straggler."""
+    import numpy as np
+    from helpers import oracle_sum, seeded_inputs
+
+    monkeypatch.delenv("STRAGGLAR_GATE", raising=False)
+    assert not sc.compile_program("stragglar", 8).main.gate_rounds
+    monkeypatch.setenv("STRAGGLAR_GATE", "1")
+    assert sc.compile_program("stragglar", 8).main.gate_rounds
+    assert not sc.compile_program("stragglar", 2).main.gate_rounds       # one round: nothing to gate
+    assert not sc.compile_program("ring", 8).main.gate_rounds            # "1" gates the synthesized schedule only
+    monkeypatch.setenv("STRAGGLAR_GATE", "all")
+    for alg, n in (("stragglar", 8), ("stragglar", 6), ("stragglar_a2a", 4), ("ring", 4), ("rhd", 8), ("direct", 4), ("rsag", 4)):
+        prog = sc.compile_program(alg, n)
+        assert prog.main.gate_rounds, alg
+        bufs = seeded_inputs(n, 20_011)
+        want = oracle_sum(bufs)
+        delay = [0.0] * n
+        delay[n - 1] = 3.0
+        assert sc.host_allreduce(prog, bufs, blocks=3, tile_elems=256, delay_ms=delay) == 0
+        for b in bufs:
+            np.testing.assert_allclose(b.astype(np.float64), want, atol=2e-5)
+        if len(prog.phases) == 1:
+            # twice in a row on the same control words (the second epoch): the sum of n equal sums
+            assert sc.host_allreduce(prog.main, bufs, blocks=3, tile_elems=256, repeats=2) == 0
+            for b in bufs:
+                np.testing.assert_allclose(b.astype(np.float64), want * n * n, rtol=1e-5, atol=1e-3)
+    monkeypatch.setenv("STRAGGLAR_GATE", "0")
+    assert not sc.compile_program("stragglar", 8).main.gate_rounds

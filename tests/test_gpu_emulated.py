@@ -213,3 +213,36 @@ def test_round_trace(path):
     comm.sync()
     assert comm.round_trace() == before
     comm.close()
+
+
+@pytest.mark.skipif(os.environ.get("STRAGGLAR_TEST_GATE", "0") != "1",
+                    reason="round gating on the GPU joins the run with STRAGGLAR_TEST_GATE=1 until it has been exercised there")
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("alg,n", [("stragglar", 8), ("stragglar", 6), ("ring", 4), ("stragglar_a2a", 4)])
+def test_round_gating(alg, n, path, monkeypatch):
+    """Rounds one after the other (STRAGGLAR_GATE): same sums, twice in a row on the same control words, and the
+    traced rounds do not overlap on any rank."""
+    from stragglar_b200 import ops
+    monkeypatch.setenv("STRAGGLAR_GATE", "all")
+    monkeypatch.setenv("STRAGGLAR_GATE_MIN_BYTES", "0")      # gate the small test buffers too
+    prog = sc.compile_program(alg, n)
+    assert prog.main.gate_rounds
+    comm = ops.LocalComm(n, emulate=True)
+    for rep in range(2):
+        xs = _inputs(n, 50_003, torch.float32)
+        want = torch.stack([x.double() for x in xs]).sum(0)
+        comm.run(prog, xs, path=path, blocks=2, tile_bytes=4096, timeout_s=5.0, trace_rounds=True)
+        comm.sync()
+        for x in xs:
+            torch.testing.assert_close(x.double(), want, **TOL[torch.float32])
+    tr = comm.round_trace()
+    starts = {}
+    ends = {}
+    for r in range(n):
+        for k, (s, e, _) in tr[r].items():
+            starts[k] = min(starts.get(k, s), s)
+            ends[k] = max(ends.get(k, e), e)
+    rounds = sorted(starts)
+    # GPUs' %globaltimer values agree here: all ranks are emulated on one device
+    assert all(ends[a] <= starts[b] for a, b in zip(rounds, rounds[1:])), (starts, ends)
+    comm.close()
