@@ -365,6 +365,9 @@ Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* 
   // STRAGGLAR_GATE=1 gates "stragglar", STRAGGLAR_GATE=all every algorithm, 0 none.
   const char* gate = getenv("STRAGGLAR_GATE");
   if (gate && *gate) p.gate_rounds = !strcmp(gate, "all") || (atoi(gate) != 0 && alg == "stragglar" && n >= 4);
+  // one round at a time there is one flow per port whatever the block count, and the model keeps
+  // improving up to 128 blocks: the cap of the free-running lowering does not apply
+  if (p.gate_rounds && alg == "stragglar") p.blocks_hint = 0;
   return p;
 }
 
