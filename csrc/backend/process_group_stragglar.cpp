@@ -286,6 +286,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.timeout_ns = (uint64_t)(opts_.timeout_s * 1e9);
       P.status = t.status(); P.trace = reinterpret_cast<uint64_t*>(t.status() + 4); P.delay_ns = 0;
       P.gate_rounds = (c.gate_rounds && count * esize >= sar::gate_min_bytes()) ? 1u : 0u;
+      P.lane1_eighths = (uint32_t)c.lane1_eighths;
       SAR_CUDA_CHECK(sar_cuda_launch(&P, opts_.path, blocks, opts_.threads, s.stream->stream()));
       ++launches_;
     } else {
@@ -300,6 +301,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       l.geom = g; l.dtype = (SarDtype)dt; l.scale = scale; l.epoch_base = epoch; l.timeout_s = opts_.timeout_s;
       l.participants = c.participants;
       l.gate_rounds = c.gate_rounds && count * esize >= sar::gate_min_bytes();
+      l.lane1_eighths = (uint32_t)c.lane1_eighths;
       const uint32_t st = sar::host_run_block(v, rt, l, 0, 1);
       if (st != SAR_OK) {
         as_atomic(&t.ctrl(me, c.channel)->abort_flag)->store(0);

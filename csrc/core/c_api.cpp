@@ -62,6 +62,7 @@ int sar_table_channel(const sar_table* t) { return t->c.channel; }
 int sar_table_blocks_hint(const sar_table* t) { return t->c.blocks_hint; }
 int sar_table_gate_rounds(const sar_table* t) { return t->c.gate_rounds ? 1 : 0; }
 uint64_t sar_gate_min_bytes(void) { return sar::gate_min_bytes(); }
+int sar_table_lane1_eighths(const sar_table* t) { return t->c.lane1_eighths; }
 uint32_t sar_table_participants(const sar_table* t) { return t->c.participants; }
 uint32_t sar_host_execute_program(const sar_program* p, void* const* bufs, uint64_t count, int dtype,
                                   uint32_t tile_elems, float scale, int blocks, const double* delay_ms,

@@ -143,7 +143,7 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   uint32_t table_lanes = 1;
   for (const SarOp& op : t.ops) if (op.lane) table_lanes = 2;
   uint32_t lanes, lane, lblock, lnblocks;
-  sar_lane_of_block((uint32_t)block, (uint32_t)nblocks, table_lanes, &lanes, &lane, &lblock, &lnblocks);
+  sar_lane_of_block((uint32_t)block, (uint32_t)nblocks, table_lanes, l.lane1_eighths, &lanes, &lane, &lblock, &lnblocks);
   const int block_all = block, nblocks_all = nblocks;
   block = (int)lblock; nblocks = (int)lnblocks;   // from here on: position inside the lane
   uint64_t item_base = 0;
@@ -292,6 +292,7 @@ static uint32_t run_phases(const std::vector<const Compiled*>& phases, void* con
               l.geom = make_geom(count, esize, c.num_chunks, te);
               l.dtype = dtype; l.scale = scale; l.timeout_s = timeout_s; l.participants = c.participants;
               l.gate_rounds = c.gate_rounds;
+              l.lane1_eighths = (uint32_t)c.lane1_eighths;
               l.epoch_base = (uint32_t)(rep + 1) * SAR_VER_STRIDE;
               l.delay_ms = (!delayed && delay_ms) ? delay_ms[r] : 0.0;
               delayed = true;

@@ -31,6 +31,7 @@ struct HostLaunch {
   double delay_ms = 0.0;                  // sleep before arriving (an injected straggler delay)
   uint32_t participants = 0;              // ranks that run this collective (exit barrier set)
   bool gate_rounds = false;               // rounds one after the other (every rank of the launch must agree)
+  uint32_t lane1_eighths = 4;             // share of the blocks of lane 1 (see sar_lane_of_block)
 };
 
 // Executes block `block` of `nblocks` of this rank's table.  Every block of

@@ -368,6 +368,10 @@ Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* 
   // one round at a time there is one flow per port whatever the block count, and the model keeps
   // improving up to 128 blocks: the cap of the free-running lowering does not apply
   if (p.gate_rounds && alg == "stragglar") p.blocks_hint = 0;
+  // share of the blocks given to the forwarding lane (eighths); half unless STRAGGLAR_LANE1_EIGHTHS says otherwise
+  // (forwarding moves n-2 chunks per chunk matched: the model of the executor prefers 5/8 at 32 blocks)
+  const char* l1 = getenv("STRAGGLAR_LANE1_EIGHTHS");
+  if (l1 && *l1 && atoi(l1) >= 1 && atoi(l1) <= 7) p.lane1_eighths = atoi(l1);
   return p;
 }
 
@@ -595,6 +599,7 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
   }
   if (out.max_version >= (int)SAR_VER_STRIDE) throw CompileError("too many versions of one slot");
   out.blocks_hint = plan.blocks_hint;
+  out.lane1_eighths = plan.lane1_eighths;
   out.gate_rounds = plan.gate_rounds;
   for (const RankTable& rt : out.ranks)
     for (const SarOp& op : rt.ops)

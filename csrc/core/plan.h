@@ -67,6 +67,7 @@ struct Plan {
   bool push_copies = false;       // lower Copy steps as SAR_PUSH (executed by the source) instead of SAR_COPY
   int blocks_hint = 0;            // largest block count per rank worth using (0: no preference)
   bool gate_rounds = false;       // run the rounds one after the other (see SAR_GATE_ALL_DONE in table.h)
+  int lane1_eighths = 4;          // two lanes: share of the blocks that forwarding (lane 1) gets, in eighths
   bool two_lanes = false;         // forwarding ops go to lane 1 (their own blocks), the rest to lane 0
   bool split_copies = false;      // forward a chunk as two half-chunk ops, interleaved tile by tile, so that
                                   // forwarding follows both halves of a straggler matching as they are produced
@@ -106,6 +107,7 @@ struct Compiled {
   int num_rounds = 0;
   int blocks_hint = 0;    // upper bound of the blocks per rank this table runs best with (0: none)
   bool gate_rounds = false;   // launch with round gating (every rank of a launch must agree)
+  int lane1_eighths = 4;      // share of the blocks of lane 1, in eighths (see sar_lane_of_block)
   std::vector<RankTable> ranks;          // by physical rank
   std::vector<int> logical_to_physical;
   // per-rank traffic in chunks (for rooflines): chunks read from peers, chunks written to peers

@@ -153,13 +153,26 @@ SAR_HD uint32_t sar_flag_index(const SarGeom& g, uint32_t chunk, uint32_t tile) 
 // that forwarding overlaps the matchings instead of queueing behind them in
 // the same blocks.  With a single block (or a one-lane table) there is one
 // lane that walks every op.
-SAR_HD void sar_lane_of_block(uint32_t block, uint32_t nblocks, uint32_t table_lanes, uint32_t* lanes,
+// `lane1_eighths` is the share of the blocks that lane 1 gets, in eighths (0 or 4: half, the
+// blocks alternate between the lanes; otherwise lane 0 takes the first blocks and lane 1 the rest,
+// at least one block each).
+SAR_HD void sar_lane_of_block(uint32_t block, uint32_t nblocks, uint32_t table_lanes, uint32_t lane1_eighths, uint32_t* lanes,
                               uint32_t* lane, uint32_t* lane_block, uint32_t* lane_nblocks) {
   const uint32_t L = (table_lanes >= 2 && nblocks >= 2) ? 2u : 1u;
   *lanes = L;
-  *lane = block % L;
-  *lane_block = block / L;
-  *lane_nblocks = (nblocks - *lane + L - 1) / L;
+  if (L == 1 || lane1_eighths == 0 || lane1_eighths == 4) {
+    *lane = block % L;
+    *lane_block = block / L;
+    *lane_nblocks = (nblocks - *lane + L - 1) / L;
+    return;
+  }
+  uint32_t n1 = (nblocks * (lane1_eighths > 7 ? 7u : lane1_eighths) + 4) / 8;
+  if (n1 < 1) n1 = 1;
+  if (n1 > nblocks - 1) n1 = nblocks - 1;
+  const uint32_t n0 = nblocks - n1;
+  *lane = block < n0 ? 0u : 1u;
+  *lane_block = block < n0 ? block : block - n0;
+  *lane_nblocks = block < n0 ? n0 : n1;
 }
 // wrap-safe "flag has reached target"
 SAR_HD bool sar_reached(uint32_t flag, uint32_t target) { return (int32_t)(flag - target) >= 0; }

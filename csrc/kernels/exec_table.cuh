@@ -243,7 +243,7 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t n
     uint32_t table_lanes = 1;
     for (uint32_t o = 0; o < nops && o < SAR_MAX_OPS; ++o) if (P.ops[o].lane) table_lanes = 2;
     uint32_t lanes, lane, lb, lnb;
-    sar_lane_of_block(0, nblocks, table_lanes, &lanes, &lane, &lb, &lnb);
+    sar_lane_of_block(0, nblocks, table_lanes, P.lane1_eighths, &lanes, &lane, &lb, &lnb);
     G.lanes = lanes;
     G.num_rounds = nrounds;
   }
@@ -273,7 +273,7 @@ struct ItemWalker {
   __device__ void init(const SarLaunchParams* p, const TableGeom* g, uint32_t b, uint32_t nb) {
     P = p; G = g; ri = 0; base_mod = 0;
     uint32_t lanes;
-    sar_lane_of_block(b, nb, g->lanes, &lanes, &lane, &block, &nblocks);
+    sar_lane_of_block(b, nb, g->lanes, p->lane1_eighths, &lanes, &lane, &block, &nblocks);
     load_round();
   }
   __device__ void load_round() {

@@ -37,6 +37,8 @@ struct SarLaunchParams {
   uint64_t* trace;        // optional: [0] = arrival time, [1] = end time (%globaltimer ns), else nullptr
   uint32_t trace_rounds;  // != 0: trace holds SAR_TRACE_WORDS words and the per-round statistics are kept
   uint32_t gate_rounds;   // != 0: the rounds run one after the other (every rank of the launch agrees; see table.h)
+  uint32_t lane1_eighths; // share of the blocks of lane 1, in eighths (0 or 4: half; see sar_lane_of_block)
+  uint32_t pad1;
   uint64_t delay_ns;      // spin this long before arriving (a late rank when ranks share one launch)
   SarMcGroup mc[2];       // multicast views (simt path): all ranks, and e.g. the non-stragglers
 };

@@ -232,6 +232,7 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       P.timeout_ns = (uint64_t)(timeout_s * 1e9);
       P.status = rk.status; P.trace = rk.trace; P.trace_rounds = o->trace_rounds ? 1u : 0u;
       P.gate_rounds = (sar_table_gate_rounds(t) && count * esize >= sar_gate_min_bytes()) ? 1u : 0u;
+      P.lane1_eighths = (uint32_t)sar_table_lane1_eighths(t);
       if (mc_alloc) {
         for (int g = 0; g < 2; ++g) {
           if (!mc_alloc->mc[g][r]) continue;

@@ -47,10 +47,15 @@ class Result:
     timeline: Dict[str, np.ndarray] = field(default_factory=dict)     # "in"/"out" -> [bin, rank] port use (0..1)
 
 
-def _lane_of_block(block: int, nblocks: int, table_lanes: int):
+def _lane_of_block(block: int, nblocks: int, table_lanes: int, lane1_eighths: int = 4):
+    """(lanes, lane, position in the lane, blocks of the lane): the rule of sar_lane_of_block (csrc/core/table.h)."""
     lanes = 2 if (table_lanes >= 2 and nblocks >= 2) else 1
-    lane = block % lanes
-    return lanes, lane, block // lanes, (nblocks - lane + lanes - 1) // lanes
+    if lanes == 1 or lane1_eighths in (0, 4):
+        lane = block % lanes
+        return lanes, lane, block // lanes, (nblocks - lane + lanes - 1) // lanes
+    n1 = max(1, min(nblocks - 1, (nblocks * min(lane1_eighths, 7) + 4) // 8))
+    n0 = nblocks - n1
+    return (lanes, 0, block, n0) if block < n0 else (lanes, 1, block - n0, n1)
 
 
 def _items_of_rank(ops: np.ndarray, num_chunks: int, chunk_tiles: List[int], tile_bytes_of, lanes: int):
@@ -108,10 +113,11 @@ def simulate(program: sc.Program, nbytes: int, blocks: int = 64, tile_bytes: int
         if not table.takes_part(r) or len(ops_of[r]) == 0:
             continue
         table_lanes = 2 if int(ops_of[r]["lane"].max()) > 0 else 1
-        lanes = _lane_of_block(0, blocks, table_lanes)[0]
+        lanes = _lane_of_block(0, blocks, table_lanes, table.lane1_eighths)[0]
         per_lane = _items_of_rank(ops_of[r], nch, chunk_tiles, tile_bytes_of, lanes)
         for lane in range(lanes):
-            nb = _lane_of_block(lane, blocks, table_lanes)[3]
+            # block 0 is in lane 0 and the last block in lane 1 under both numbering rules
+            nb = _lane_of_block(0 if lane == 0 else blocks - 1, blocks, table_lanes, table.lane1_eighths)[3]
             t0 = delay_us[r] if delay_us else 0.0
             if dispatch == "static":
                 for b in range(nb):

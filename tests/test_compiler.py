@@ -248,3 +248,35 @@ def test_round_gating_attribute_and_host_execution(monkeypatch):
                 np.testing.assert_allclose(b.astype(np.float64), want * n * n, rtol=1e-5, atol=1e-3)
     monkeypatch.setenv("STRAGGLAR_GATE", "0")
     assert not sc.compile_program("stragglar", 8).main.gate_rounds
+
+
+def test_lane_split_share(monkeypatch):
+    """STRAGGLAR_LANE1_EIGHTHS moves blocks between the two lanes: every split runs to the same sums, the default
+    (half, alternating) is unchanged, and the split covers every block exactly once."""
+    import numpy as np
+    from helpers import oracle_sum, seeded_inputs
+    from stragglar_b200.exec_model import _lane_of_block
+
+    for nblocks in (2, 3, 8, 32, 33):
+        for e in (0, 1, 3, 4, 5, 7):
+            seen = {0: [], 1: []}
+            for b in range(nblocks):
+                lanes, lane, pos, count = _lane_of_block(b, nblocks, 2, e)
+                assert lanes == 2 and 0 <= pos < count
+                seen[lane].append((pos, count))
+            for lane in (0, 1):
+                assert seen[lane], (nblocks, e)
+                assert sorted(p for p, _ in seen[lane]) == list(range(seen[lane][0][1]))
+            if e in (0, 4):
+                assert len(seen[0]) == (nblocks + 1) // 2
+    monkeypatch.delenv("STRAGGLAR_LANE1_EIGHTHS", raising=False)
+    assert sc.compile_program("stragglar_a2a", 8).main.lane1_eighths == 4
+    for e in ("2", "5", "7"):
+        monkeypatch.setenv("STRAGGLAR_LANE1_EIGHTHS", e)
+        prog = sc.compile_program("stragglar_a2a", 6)
+        assert prog.main.lane1_eighths == int(e)
+        bufs = seeded_inputs(6, 12_345)
+        want = oracle_sum(bufs)
+        assert sc.host_allreduce(prog, bufs, blocks=5, tile_elems=128) == 0
+        for b in bufs:
+            np.testing.assert_allclose(b.astype(np.float64), want, atol=2e-5)
