@@ -47,3 +47,35 @@ def test_bench_py_reference_arm_without_the_program(tmp_path):
     assert p.returncode == 0
     out = json.loads(p.stdout.strip().splitlines()[-1])
     assert out["impl"] == "reference" and "unavailable" in out
+
+
+def test_tune_ranks_settings_with_a_fake_program(tmp_path, monkeypatch, capsys):
+    """bench/tune.py: runs one program per setting, reads the CSV, ranks the settings per algorithm and size."""
+    import importlib.util
+    import stat
+    import sys
+    spec = importlib.util.spec_from_file_location("tune", os.path.join(ROOT, "bench", "tune.py"))
+    tune = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tune)
+    fake = tmp_path / "allreduce"
+    # time = size / blocks, gating takes a fifth off; one setting fails
+    fake.write_text("#!/usr/bin/env python3\n"
+                    "import os, sys\n"
+                    "sizes, alg, iters, delay = sys.argv[1].split(','), sys.argv[2], int(sys.argv[3]), sys.argv[4]\n"
+                    "b = int(os.environ.get('STRAGGLAR_BLOCKS', '128'))\n"
+                    "if os.environ.get('STRAGGLAR_PATH') == 'simta': sys.stderr.write('collective failed\\n'); sys.exit(2)\n"
+                    "print('algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s),n,dtype,path,time_us_max,algbw_GBps,busbw_GBps,roofline_frac,real_delay_ms')\n"
+                    "for s in sizes:\n"
+                    "    for i in range(iters):\n"
+                    "        ms = int(s) / 1e6 / b * (0.8 if os.environ.get('STRAGGLAR_GATE') == '1' else 1.0)\n"
+                    "        print(f'{alg},{s},{i+1},{delay},{ms:.3f},1.0,8,float32,tma,0,0,0,0,0.000')\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setattr(tune, "EXE", str(fake))
+    monkeypatch.setattr(sys, "argv", ["tune.py", "--sizes", "1048576,2097152", "--iters", "3", "--out", str(tmp_path / "raw")])
+    assert tune.main() == 0
+    out = capsys.readouterr().out
+    block = out.split("stragglar, 1 MiB (net ms, best first)")[1].split("stragglar, 2 MiB")[0]
+    ranked = [l.split(None, 1)[1] for l in block.strip().splitlines()]
+    assert ranked[0] == "blocks=128 gate=1" and ranked[1] == "blocks=128"
+    assert "path=simta blocks=64 [FAILED: collective failed]" in out
+    assert (tmp_path / "raw" / "stragglar_blocks128_gate1.csv").exists()
