@@ -177,6 +177,8 @@ def simulate(program: sc.Program, nbytes: int, blocks: int = 64, tile_bytes: int
                 if not round_gate_open(int(op_["round"]), now):
                     return False
                 for q in range(int(op_["nsrc"])):
+                    if delay_us and delay_us[int(op_["src"][q])] > now:
+                        return False          # the peer has not entered the collective yet (its arrival word)
                     v = int(op_["src_ver"][q])
                     if v and ready_at.get((int(op_["src"][q]), c_, t_, v), np.inf) > now:
                         return False
@@ -325,6 +327,8 @@ def main(argv=None) -> int:
     ap.add_argument("--link-gbs", type=float, default=770.0)
     ap.add_argument("--block-gbs", type=float, default=64.0)
     ap.add_argument("--flag-us", type=float, default=3.0)
+    ap.add_argument("--delay-ms", type=float, default=0.0,
+                    help="hold the straggler back this long (with the pre-phase in the table: what DELAY > 0 times)")
     ap.add_argument("--rounds", action="store_true", help="print when every schedule round started and ended")
     ap.add_argument("--dispatch", default="static", choices=["static", "dynamic"],
                     help="static: block b owns items b, b+G, ... (the kernels); dynamic: free blocks take the next item")
@@ -335,10 +339,16 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     prog = sc.compile_program(args.alg, args.n, prephase=not args.no_prephase, straggler=args.straggler)
     blocks = args.blocks or (prog.main.blocks_hint if prog.main.blocks_hint > 0 else 128)
+    delay = None
+    if args.delay_ms > 0:
+        delay = [0.0] * args.n
+        delay[args.straggler if args.straggler is not None else args.n - 1] = args.delay_ms * 1e3
     res = simulate(prog, args.bytes, blocks, args.tile_bytes,
-                   ModelParams(link_gbs=args.link_gbs, block_gbs=args.block_gbs, flag_us=args.flag_us),
+                   ModelParams(link_gbs=args.link_gbs, block_gbs=args.block_gbs, flag_us=args.flag_us), delay_us=delay,
                    timeline_us=args.timeline, dispatch=args.dispatch, window=args.window, round_lag=args.round_lag)
     link = prog.link_bytes(args.bytes) / (args.link_gbs * 1e3)
+    if delay:
+        print(f"straggler held back {args.delay_ms:g} ms: {res.time_us - args.delay_ms * 1e3:.1f} us after its arrival")
     print(f"{args.alg} n={args.n} {args.bytes} bytes, {blocks} blocks: {res.time_us:.1f} us modelled, "
           f"{link:.1f} us at the busiest port's rate ({link / res.time_us:.2f}), {res.items} items")
     print("port use in:  " + " ".join(f"{x:.2f}" for x in res.port_busy["in"]))

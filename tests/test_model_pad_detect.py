@@ -209,3 +209,6 @@ def test_tile_level_model_of_the_executor(monkeypatch):
     monkeypatch.delenv("STRAGGLAR_GATE")
     dyn = simulate(prog, nbytes, blocks=32, dispatch="dynamic", window=4, params=ModelParams(flag_us=1.0, block_gbs=128.0))
     assert dyn.time_us > floor
+    # a straggler that is later than the pre-phase takes: what remains after its arrival is what DELAY -1 times
+    late = simulate(sc.compile_program("stragglar", 8), nbytes, blocks=32, delay_us=[0.0] * 7 + [5000.0])
+    assert abs((late.time_us - 5000.0) - free.time_us) < 0.02 * free.time_us
