@@ -329,6 +329,12 @@ int64_t ProcessGroupStragglar::check_status(bool cuda) {
   return st;
 }
 
+bool ProcessGroupStragglar::check_guards(bool cuda) {
+  std::lock_guard<std::mutex> lk(mu_);
+  Side& s = cuda ? cuda_ : cpu_;
+  return !s.t || s.t->check_guards();
+}
+
 std::pair<int64_t, int64_t> ProcessGroupStragglar::last_trace() {
   Side& s = cuda_;
   if (!s.t) return {0, 0};
@@ -918,6 +924,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("check_status", [](const c10::intrusive_ptr<c10d::Backend>& b, bool cuda) { return cast(b)->check_status(cuda); },
         py::arg("backend"), py::arg("cuda") = true, py::call_guard<py::gil_scoped_release>());
   m.def("launches", [](const c10::intrusive_ptr<c10d::Backend>& b) { return cast(b)->launches(); });
+  m.def("check_guards", [](const c10::intrusive_ptr<c10d::Backend>& b, bool cuda) { return cast(b)->check_guards(cuda); },
+        py::arg("backend"), py::arg("cuda") = true, py::call_guard<py::gil_scoped_release>());
   m.def("last_trace", [](const c10::intrusive_ptr<c10d::Backend>& b) { return cast(b)->last_trace(); },
         py::call_guard<py::gil_scoped_release>());
 }

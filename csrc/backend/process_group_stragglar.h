@@ -130,6 +130,8 @@ class ProcessGroupStragglar : public c10d::Backend {
   // (a SarStatus; 0 = ok), clearing a recorded failure.
   int64_t check_status(bool cuda);
   int64_t launches() const { return launches_; }   // kernels of this library launched so far
+  // True while the canary bytes around this rank's data region (symmetric heap + staging) are intact.
+  bool check_guards(bool cuda);
   // %globaltimer stamps (ns) of the last collective kernel of this rank: when it arrived and
   // when it left.  Their difference is the time the rank spent inside the collective; the
   // persistent straggler is the rank that spends the least (it arrives last and waits for nobody).

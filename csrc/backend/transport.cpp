@@ -29,7 +29,7 @@ Transport::Transport(bool cuda, int device, int rank, int n, size_t data_bytes, 
   TORCH_CHECK(n >= 1 && n <= SAR_MAX_RANKS, "stragglar backend supports up to ", SAR_MAX_RANKS, " ranks, got ", n);
   data_bytes_ = (data_bytes + 4095) / 4096 * 4096;
   staging_bytes_ = std::min(data_bytes_, (staging_bytes + 4095) / 4096 * 4096);
-  total_bytes_ = ArenaLayout::kDataOff + data_bytes_;
+  total_bytes_ = ArenaLayout::kDataOff + data_bytes_ + ArenaLayout::kGuardBytes;
   heap_ = std::make_shared<Heap>(heap_bytes());
   try {
     open_arenas(store, prefix);
@@ -49,6 +49,8 @@ void Transport::open_arenas(const c10::intrusive_ptr<c10d::Store>& store, const 
     void* p = nullptr;
     SAR_CUDA_CHECK(cudaMalloc(&p, total_bytes_));
     SAR_CUDA_CHECK(cudaMemset(p, 0, ArenaLayout::kDataOff));
+    SAR_CUDA_CHECK(cudaMemset((char*)p + ArenaLayout::kDataOff - ArenaLayout::kGuardBytes, ArenaLayout::kGuardByte, ArenaLayout::kGuardBytes));
+    SAR_CUDA_CHECK(cudaMemset((char*)p + ArenaLayout::kDataOff + data_bytes_, ArenaLayout::kGuardByte, ArenaLayout::kGuardBytes));
     SAR_CUDA_CHECK(cudaDeviceSynchronize());
     base_[rank] = (char*)p;
     if (n > 1) {
@@ -76,6 +78,8 @@ void Transport::open_arenas(const c10::intrusive_ptr<c10d::Store>& store, const 
     close(fd);
     TORCH_CHECK(p != MAP_FAILED, "mmap failed: ", strerror(errno));
     base_[rank] = (char*)p;   // fresh shared memory reads as zero
+    memset((char*)p + ArenaLayout::kDataOff - ArenaLayout::kGuardBytes, ArenaLayout::kGuardByte, ArenaLayout::kGuardBytes);
+    memset((char*)p + ArenaLayout::kDataOff + data_bytes_, ArenaLayout::kGuardByte, ArenaLayout::kGuardBytes);
     store->set(me, to_bytes(shm_name_.data(), shm_name_.size()));
     for (int r = 0; r < n; ++r) {
       if (r == rank) continue;
@@ -109,6 +113,23 @@ void Transport::release() {
       if (base_[r]) munmap(base_[r], total_bytes_);
   }
   for (int r = 0; r < n_; ++r) base_[r] = nullptr;
+}
+
+bool Transport::check_guards() const {
+  unsigned char g[2 * ArenaLayout::kGuardBytes];
+  const char* lo = base_[rank_] + ArenaLayout::kDataOff - ArenaLayout::kGuardBytes;
+  const char* hi = base_[rank_] + ArenaLayout::kDataOff + data_bytes_;
+  if (cuda_) {
+    if (cudaSetDevice(device_) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) return false;
+    if (cudaMemcpy(g, lo, ArenaLayout::kGuardBytes, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+    if (cudaMemcpy(g + ArenaLayout::kGuardBytes, hi, ArenaLayout::kGuardBytes, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+  } else {
+    memcpy(g, lo, ArenaLayout::kGuardBytes);
+    memcpy(g + ArenaLayout::kGuardBytes, hi, ArenaLayout::kGuardBytes);
+  }
+  for (unsigned char b : g)
+    if (b != ArenaLayout::kGuardByte) return false;
+  return true;
 }
 
 int64_t Transport::heap_offset(const void* p, size_t bytes) const {

@@ -1,7 +1,9 @@
 // Symmetric arenas of a process group, as one rank sees them.
 //
 // Every rank owns one region with the same layout:
-//   [control words | status | flags (all channels) | data]
+//   [control words | status | flags (all channels) | guard | data | guard]
+// (the guards are canary bytes on both sides of the data region; check_guards() tells whether a
+// kernel or a copy has written outside the region)
 // and maps every peer's region into its own address space: CUDA IPC handles
 // for device memory, POSIX shared memory for host memory.  The handles (or
 // names) travel through the c10d Store the process group was given; the
@@ -27,7 +29,9 @@ struct ArenaLayout {
   static constexpr size_t kStatusOff = 2048;
   static constexpr size_t kFlagsOff = 4096;
   static constexpr size_t kFlagsBytes = sizeof(uint32_t) * (size_t)SAR_NUM_CHANNELS * SAR_FLAG_CAPACITY;
-  static constexpr size_t kDataOff = kFlagsOff + kFlagsBytes;
+  static constexpr size_t kGuardBytes = 256;
+  static constexpr unsigned char kGuardByte = 0xA5;
+  static constexpr size_t kDataOff = kFlagsOff + kFlagsBytes + kGuardBytes;
 };
 
 // Bookkeeping of the symmetric heap.  Shared with the deleters of the tensors handed out, so that a
@@ -65,6 +69,10 @@ class Transport {
   size_t staging_bytes() const { return staging_bytes_; }
   size_t staging_off() const { return data_bytes_ - staging_bytes_; }   // staging sits at the end of the data region
   size_t heap_bytes() const { return data_bytes_ - staging_bytes_; }
+
+  // True while the canary bytes before and after this rank's data region are intact (waits for the
+  // device first).  A false answer means something wrote outside the region it was given.
+  bool check_guards() const;
 
   // next epoch base of a channel (every rank calls this in the same order)
   uint32_t next_epoch(int channel) { return epoch_[channel] += SAR_VER_STRIDE; }

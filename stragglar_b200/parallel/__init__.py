@@ -109,6 +109,13 @@ def check_status(device="cuda", group=None) -> int:
     return _ext().check_status(backend_of(device, group), torch.device(device).type == "cuda")
 
 
+def check_guards(device="cuda", group=None) -> bool:
+    """True while the canary bytes on both sides of this rank's data region (symmetric heap and staging area)
+    are intact, i.e. no kernel or copy of the backend has written outside the region."""
+    import torch
+    return bool(_ext().check_guards(backend_of(device, group), torch.device(device).type == "cuda"))
+
+
 def launches(device="cuda", group=None) -> int:
     """Number of this library's kernels the backend has launched so far."""
     return _ext().launches(backend_of(device, group))

@@ -145,6 +145,8 @@ def _collectives(rank, world):
         [torch.full((2,), float(rank)), torch.full((4,), float(rank + 10))], dist.group.WORLD)]
     assert torch.equal(gouts[0], torch.arange(world).repeat_interleave(2).float())
     assert torch.equal(gouts[1], (torch.arange(world) + 10).repeat_interleave(4).float())
+    # the canary bytes on both sides of the heap + staging region are intact after all of the above
+    assert sp.check_guards("cpu") and sp.check_status("cpu") == 0
 
 
 @pytest.mark.parametrize("world", [2, 4])

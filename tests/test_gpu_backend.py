@@ -75,6 +75,7 @@ def _cuda_collectives(rank, world):
     torch.cuda.synchronize()
     assert sp.check_status(dev) == 0
     assert sp.launches(dev) > 0
+    assert sp.check_guards(dev)      # nothing wrote outside the heap and the staging area
 
 
 def test_backend_world1_on_one_gpu():
