@@ -264,6 +264,8 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       auto key = std::make_pair((const void*)&c, me);
       auto it = s.uploaded.find(key);
       if (it == s.uploaded.end()) {
+        const std::string why = sar::validate_rank_table(rt, me, n, c.num_chunks);
+        TORCH_CHECK(why.empty(), "stragglar backend: refusing to launch a malformed table: ", why);
         void *d_ops = nullptr, *d_rb = nullptr;
         SAR_CUDA_CHECK(cudaMalloc(&d_ops, std::max<size_t>(1, rt.ops.size()) * sizeof(SarOp)));
         SAR_CUDA_CHECK(cudaMalloc(&d_rb, std::max<size_t>(1, rt.round_begin.size()) * sizeof(uint16_t)));

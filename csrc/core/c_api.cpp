@@ -63,6 +63,13 @@ int sar_table_blocks_hint(const sar_table* t) { return t->c.blocks_hint; }
 int sar_table_gate_rounds(const sar_table* t) { return t->c.gate_rounds ? 1 : 0; }
 uint64_t sar_gate_min_bytes(void) { return sar::gate_min_bytes(); }
 int sar_table_lane1_eighths(const sar_table* t) { return t->c.lane1_eighths; }
+int sar_table_validate(const sar_table* t, int rank, int nranks, char* err, int errlen) {
+  if (rank < 0 || rank >= (int)t->c.ranks.size()) { if (err && errlen > 0) snprintf(err, (size_t)errlen, "no table for rank %d", rank); return 1; }
+  const std::string why = sar::validate_rank_table(t->c.ranks[rank], rank, nranks, t->c.num_chunks);
+  if (why.empty()) return 0;
+  if (err && errlen > 0) snprintf(err, (size_t)errlen, "%s", why.c_str());
+  return 1;
+}
 uint32_t sar_table_participants(const sar_table* t) { return t->c.participants; }
 uint32_t sar_host_execute_program(const sar_program* p, void* const* bufs, uint64_t count, int dtype,
                                   uint32_t tile_elems, float scale, int blocks, const double* delay_ms,

@@ -600,6 +600,10 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
   if (out.max_version >= (int)SAR_VER_STRIDE) throw CompileError("too many versions of one slot");
   out.blocks_hint = plan.blocks_hint;
   out.lane1_eighths = plan.lane1_eighths;
+  for (int r = 0; r < (int)out.ranks.size(); ++r) {
+    const std::string why = validate_rank_table(out.ranks[r], r, np, P);
+    if (!why.empty()) throw CompileError(plan.name + ": table of rank " + std::to_string(r) + " is malformed: " + why);
+  }
   out.gate_rounds = plan.gate_rounds;
   for (const RankTable& rt : out.ranks)
     for (const SarOp& op : rt.ops)
@@ -655,6 +659,44 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
   return out;
 }
 
+
+std::string validate_rank_table(const RankTable& t, int rank, int nranks, int num_chunks) {
+  auto bad = [&](size_t o, const std::string& what) { return "op " + std::to_string(o) + ": " + what; };
+  if (t.ops.size() > SAR_MAX_OPS) return "more than " + std::to_string(SAR_MAX_OPS) + " ops";
+  if (t.ops.empty()) return t.round_begin.size() <= 1 ? "" : "round list of an empty table";
+  if (t.round_begin.size() < 2 || t.round_begin.front() != 0 || t.round_begin.back() != t.ops.size())
+    return "round list does not cover the ops";
+  if (t.round_begin.size() - 1 > SAR_MAX_ROUNDS) return "more than " + std::to_string(SAR_MAX_ROUNDS) + " rounds";
+  for (size_t i = 0; i + 1 < t.round_begin.size(); ++i) {
+    if (t.round_begin[i] >= t.round_begin[i + 1]) return "empty or unsorted round " + std::to_string(i);
+    for (size_t o = t.round_begin[i]; o < t.round_begin[i + 1]; ++o) {
+      if (t.ops[o].round != t.ops[t.round_begin[i]].round) return bad(o, "round differs inside a round");
+      if (o > t.round_begin[i] && t.ops[o].lane < t.ops[o - 1].lane) return bad(o, "lanes unsorted inside a round");
+    }
+    if (i > 0 && t.ops[t.round_begin[i]].round <= t.ops[t.round_begin[i - 1]].round) return "rounds not increasing";
+  }
+  for (size_t o = 0; o < t.ops.size(); ++o) {
+    const SarOp& op = t.ops[o];
+    if (op.kind > SAR_PUSH) return bad(o, "unknown kind");
+    if ((int)op.chunk >= num_chunks) return bad(o, "chunk out of range");
+    if (op.parts == 0 || op.part >= op.parts) return bad(o, "bad tile range");
+    if (op.lane > 1) return bad(o, "bad lane");
+    if (op.nsrc > SAR_MAX_RANKS || (int)op.nsrc >= std::max(nranks, 2)) return bad(o, "too many peers");
+    if ((op.kind == SAR_COPY || op.kind == SAR_REDUCE_PUSH) && op.nsrc != 1) return bad(o, "needs exactly one peer");
+    if (op.kind == SAR_PUSH && op.nsrc == 0) return bad(o, "push without a destination");
+    uint32_t seen = 0;
+    for (int q = 0; q < op.nsrc; ++q) {
+      if ((int)op.src[q] >= nranks) return bad(o, "peer out of range");
+      if ((int)op.src[q] == rank) return bad(o, "names the rank itself as a peer");
+      if (seen >> op.src[q] & 1) return bad(o, "names a peer twice");
+      seen |= 1u << op.src[q];
+      if (op.src_ver[q] >= SAR_VER_STRIDE) return bad(o, "version out of range");
+    }
+    if (op.local_ver >= SAR_VER_STRIDE || op.post_ver >= SAR_VER_STRIDE || op.push_ver >= SAR_VER_STRIDE)
+      return bad(o, "version out of range");
+  }
+  return "";
+}
 
 Program build_program(const std::string& alg, int n, bool prephase, int straggler, const Schedule* sched) {
   Program prog;

@@ -126,6 +126,13 @@ struct CompileError : std::runtime_error {
 // the expected one.
 Compiled compile(const Plan& plan, const std::vector<int>& logical_to_physical = {}, int n_physical = 0);
 
+// Structural check of a rank's table before it is handed to a kernel: op kinds, chunk and peer
+// indices in range, no peer named twice or equal to the rank itself, tile ranges well-formed,
+// rounds sorted and covered by round_begin, sizes within what the kernels hold in shared memory.
+// The data a table came from was hazard-checked by compile(); this catches a table that was
+// damaged or built for another communicator on its way to the device.  Returns "" or the reason.
+std::string validate_rank_table(const RankTable& t, int rank, int nranks, int num_chunks);
+
 // A collective as the user names it: one or two compiled phases launched back
 // to back.  Everything is a single phase except `direct` with its pre-phase,
 // where the non-stragglers first all-reduce among themselves on channel 1

@@ -25,8 +25,35 @@ static float uniform(uint64_t seed, uint64_t i) {
   return (float)(uint32_t)(x >> 40) * (2.0f / 16777216.0f) - 1.0f;
 }
 
+// validate_rank_table accepts what the compiler makes and names what is wrong with a damaged table
+static int check_validation() {
+  int failures = 0;
+  const sar::Program prog = sar::build_program("stragglar", 8, true, -1, nullptr);
+  const sar::Compiled& c = prog.phases.back();
+  for (int r = 0; r < 8; ++r)
+    if (!sar::validate_rank_table(c.ranks[r], r, 8, c.num_chunks).empty()) { printf("intact table of rank %d refused\n", r); ++failures; }
+  struct Case { const char* what; void (*damage)(sar::RankTable&); };
+  const Case cases[] = {
+      {"chunk", [](sar::RankTable& t) { t.ops[1].chunk = 200; }},
+      {"peer", [](sar::RankTable& t) { t.ops[0].src[0] = 9; }},
+      {"self", [](sar::RankTable& t) { t.ops[0].src[0] = 3; }},
+      {"kind", [](sar::RankTable& t) { t.ops[2].kind = 7; }},
+      {"parts", [](sar::RankTable& t) { t.ops[0].part = t.ops[0].parts; }},
+      {"rounds", [](sar::RankTable& t) { t.round_begin.back() += 1; }},
+      {"order", [](sar::RankTable& t) { std::swap(t.ops.front(), t.ops.back()); }},
+      {"version", [](sar::RankTable& t) { t.ops[0].post_ver = 40; }},
+  };
+  for (const Case& k : cases) {
+    sar::RankTable t = c.ranks[3];
+    k.damage(t);
+    if (sar::validate_rank_table(t, 3, 8, c.num_chunks).empty()) { printf("damaged table accepted (%s)\n", k.what); ++failures; }
+  }
+  if (sar::validate_rank_table(c.ranks[3], 3, 4, c.num_chunks).empty()) { printf("table for 8 ranks accepted for 4\n"); ++failures; }
+  return failures;
+}
+
 int main() {
-  int failures = 0, runs = 0;
+  int failures = check_validation(), runs = 0;
   const char* algs[] = {"stragglar", "stragglar_a2a", "ring", "rhd", "direct", "rsag"};
   // round gating (rounds one after the other) is run for every algorithm too, on the lowerings that ship
   for (const char* gate : {"0", "all"})

@@ -82,6 +82,13 @@ static DevTable* upload(Rank& rk, const sar_table* t, int rank, char* err, int e
   auto it = rk.tables.find(key);
   if (it != rk.tables.end()) return &it->second;
   DevTable* fail_value = nullptr;
+  {
+    char why[200] = "";
+    if (sar_table_validate(t, rank, sar_table_nranks(t), why, sizeof why)) {
+      if (err && errlen > 0) snprintf(err, errlen, "refusing to launch a malformed table (%s): %s", sar_status_string(SAR_BAD_TABLE), why);
+      return nullptr;
+    }
+  }
   DevTable d;
   CK(cudaMalloc(&d.ops, sizeof(SarOp) * (nops > 0 ? nops : 1)));
   CK(cudaMalloc(&d.round_begin, sizeof(uint16_t) * (nrb > 0 ? nrb : 1)));
