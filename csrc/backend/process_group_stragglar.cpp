@@ -139,10 +139,13 @@ const sar::Program& ProcessGroupStragglar::program(size_t bytes) {
 
 void ProcessGroupStragglar::set_straggler(int r) {
   TORCH_CHECK(r >= -1 && r < getSize(), "straggler rank out of range");
+  std::lock_guard<std::mutex> lk(mu_);
+  const int old = opts_.straggler;
   opts_.straggler = r;
-  (void)program();
+  try { (void)program(); } catch (...) { opts_.straggler = old; throw; }
 }
 void ProcessGroupStragglar::set_algorithm(const std::string& alg) {
+  std::lock_guard<std::mutex> lk(mu_);   // collectives read the options and the program cache under this lock
   const std::string old = opts_.alg;
   opts_.alg = alg;
   try { (void)program(); } catch (...) { opts_.alg = old; throw; }
