@@ -82,7 +82,7 @@ def _items_of_rank(ops: np.ndarray, num_chunks: int, chunk_tiles: List[int], til
     return out
 
 
-def simulate(program: sc.Program, nbytes: int, blocks: int = 64, tile_bytes: int = 65536,
+def simulate(program: sc.Program, nbytes: int, blocks: int = 64, tile_bytes: int = 0,
              params: Optional[ModelParams] = None, phase: int = -1, delay_us: Optional[List[float]] = None,
              timeline_us: float = 0.0, dispatch: str = "static", window: int = 1,
              round_lag: Optional[int] = None) -> Result:
@@ -98,6 +98,8 @@ def simulate(program: sc.Program, nbytes: int, blocks: int = 64, tile_bytes: int
     if round_lag is None and table.gate_rounds and nbytes >= sc.gate_min_bytes():
         round_lag = 0                      # the table is launched with round gating
     n, nch = table.n, table.num_chunks
+    if tile_bytes <= 0:   # the tile the library picks for fp32 on the bulk-copy path (at most 64 KiB)
+        tile_bytes = 4 * sc.pick_tile_elems(nbytes // 4, 4, nch, blocks, 2048, 65536)
     chunk_bytes = [nbytes // nch + (1 if c < (nbytes % nch) else 0) for c in range(nch)]
     chunk_tiles = [max(1, -(-cb // tile_bytes)) for cb in chunk_bytes]
 
@@ -321,7 +323,7 @@ def main(argv=None) -> int:
     ap.add_argument("n", type=int)
     ap.add_argument("--bytes", type=int, default=1 << 28)
     ap.add_argument("--blocks", type=int, default=0, help="blocks per rank (0: the table's hint, else 128)")
-    ap.add_argument("--tile-bytes", type=int, default=65536)
+    ap.add_argument("--tile-bytes", type=int, default=0, help="0: what the library picks (at most 64 KiB)")
     ap.add_argument("--no-prephase", action="store_true", help="the state after the straggler's arrival (DELAY = -1)")
     ap.add_argument("--straggler", type=int, default=None)
     ap.add_argument("--link-gbs", type=float, default=770.0)
