@@ -188,12 +188,13 @@ def test_tile_level_model_of_the_executor(monkeypatch):
     from stragglar_b200.exec_model import ModelParams, simulate
     monkeypatch.delenv("STRAGGLAR_GATE", raising=False)
     nbytes = 96 << 20
-    two = simulate(sc.compile_program("stragglar", 2, prephase=False), nbytes, blocks=32)
+    coarse = ModelParams(dt_us=0.5)          # half the steps of the default
+    two = simulate(sc.compile_program("stragglar", 2, prephase=False), nbytes, blocks=32, params=coarse)
     link_us = nbytes / (770.0 * 1e3)
     assert 0.85 < link_us / two.time_us <= 1.0
     prog = sc.compile_program("stragglar", 8, prephase=False)
-    free = simulate(prog, nbytes, blocks=32, timeline_us=50.0)
-    gated = simulate(prog, nbytes, blocks=32, round_lag=0)
+    free = simulate(prog, nbytes, blocks=32, timeline_us=50.0, params=coarse)
+    gated = simulate(prog, nbytes, blocks=32, round_lag=0, params=coarse)
     floor = prog.link_bytes(nbytes) / (770.0 * 1e3)
     assert floor < gated.time_us < free.time_us
     assert free.items == gated.items and len(free.per_rank_us) == 8
@@ -204,11 +205,11 @@ def test_tile_level_model_of_the_executor(monkeypatch):
     assert max(free.port_busy["out"]) <= 1.0 + 1e-6
     # a table compiled with gating is modelled with gating; dynamic dispatch and other constants run
     monkeypatch.setenv("STRAGGLAR_GATE", "1")
-    auto = simulate(sc.compile_program("stragglar", 8, prephase=False), nbytes, blocks=32)
+    auto = simulate(sc.compile_program("stragglar", 8, prephase=False), nbytes, blocks=32, params=coarse)
     assert abs(auto.time_us - gated.time_us) < 1e-6
     monkeypatch.delenv("STRAGGLAR_GATE")
-    dyn = simulate(prog, nbytes, blocks=32, dispatch="dynamic", window=4, params=ModelParams(flag_us=1.0, block_gbs=128.0))
+    dyn = simulate(prog, nbytes, blocks=32, dispatch="dynamic", window=4, params=ModelParams(flag_us=1.0, block_gbs=128.0, dt_us=0.5))
     assert dyn.time_us > floor
     # a straggler that is later than the pre-phase takes: what remains after its arrival is what DELAY -1 times
-    late = simulate(sc.compile_program("stragglar", 8), nbytes, blocks=32, delay_us=[0.0] * 7 + [5000.0])
-    assert abs((late.time_us - 5000.0) - free.time_us) < 0.02 * free.time_us
+    late = simulate(sc.compile_program("stragglar", 8), nbytes, blocks=32, delay_us=[0.0] * 7 + [1500.0], params=coarse)
+    assert abs((late.time_us - 1500.0) - free.time_us) < 0.02 * free.time_us
