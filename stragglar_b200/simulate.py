@@ -14,6 +14,12 @@ StragglAR rounds for n GPUs:
              3-2 elimination of Rabenseifner & Traff)
   ring       2(n-1)*a + 2(n-1)/n * S*b
   direct     log2(n)*a + log2(n) * S*b
+
+``--table`` prints absolute times per n, with the two algorithms this library adds for a switched box
+(every GPU reaches every peer at the full port rate):
+
+  stragglar_a2a  3*a + S*b            all matchings at once, then a direct all-gather: S per direction per GPU
+  rsag           2*a + 2(n-1)/n * S*b   one-shot reduce-scatter + all-gather (the ring's bytes in two steps)
 """
 from __future__ import annotations
 
@@ -86,13 +92,28 @@ def compute_speedups(N: Iterable[int], model: LinkModel = LinkModel(), rounds: O
             [1.0 for _ in ring])
 
 
+def compute_costs_switched(N: Iterable[int], model: LinkModel = LinkModel()):
+    """Per-n cost in ms of (stragglar_a2a, rsag): the algorithms that rely on a full-bandwidth switch."""
+    a, b, s = model.alpha_ms, model.beta_ms_per_byte, model.size_bytes
+    return [3 * a + s * b for _ in N], [2 * a + (2 * (n - 1) / n) * s * b for n in N]
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--b200", action="store_true", help="use NVLink 5 constants instead of the reference's")
     ap.add_argument("--nominal", action="store_true", help="with --b200: 900 GB/s instead of the measured 770")
     ap.add_argument("--size", type=int, default=GIB, help="buffer bytes (default 1 GiB)")
+    ap.add_argument("--table", action="store_true", help="absolute times in ms per n instead of the two speedup lines")
     args = ap.parse_args(argv)
     model = LinkModel.b200(not args.nominal, args.size) if args.b200 else LinkModel(size_bytes=args.size)
+    if args.table:
+        N = sorted(POWERS_OF_TWO + IN_BETWEEN)
+        sar, rhd, ring, direct = compute_costs(N, model)
+        a2a, rsag = compute_costs_switched(N, model)
+        print(f"{'n':>4s} {'stragglar':>10s} {'a2a':>8s} {'ring':>8s} {'rhd':>8s} {'rsag':>8s} {'direct':>8s}   (ms)")
+        for i, n in enumerate(N):
+            print(f"{n:4d} {sar[i]:10.3f} {a2a[i]:8.3f} {ring[i]:8.3f} {rhd[i]:8.3f} {rsag[i]:8.3f} {direct[i]:8.3f}")
+        return 0
     p = compute_speedups(POWERS_OF_TWO, model)
     q = compute_speedups(IN_BETWEEN, model)
     print("Speedups for powers of two:", *p)

@@ -213,3 +213,16 @@ def test_tile_level_model_of_the_executor(monkeypatch):
     # a straggler that is later than the pre-phase takes: what remains after its arrival is what DELAY -1 times
     late = simulate(sc.compile_program("stragglar", 8), nbytes, blocks=32, delay_us=[0.0] * 7 + [1500.0], params=coarse)
     assert abs((late.time_us - 1500.0) - free.time_us) < 0.02 * free.time_us
+
+
+def test_simulate_table_with_the_switched_algorithms(capsys):
+    from stragglar_b200 import simulate
+    assert simulate.main(["--b200", "--table"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert lines[0].split()[:4] == ["n", "stragglar", "a2a", "ring"] and len(lines) == 1 + 13
+    row8 = dict(zip(lines[0].split(), lines[[l.split()[0] for l in lines].index("8")].split()))
+    # 1 GiB at 770 GB/s: S*b = 1.394 ms; a2a moves S per direction, the ring 1.75 S, StragglAR 9/7 S
+    assert abs(float(row8["a2a"]) - 1.400) < 2e-3 and abs(float(row8["ring"]) - 2.468) < 2e-3
+    assert abs(float(row8["stragglar"]) - (9 * 0.002 + 9 / 7 * 1.39445)) < 2e-3
+    a2a, rsag = simulate.compute_costs_switched([4, 8], simulate.LinkModel.b200())
+    assert a2a[0] == a2a[1] and rsag[0] < rsag[1]
