@@ -1,6 +1,7 @@
 """Tile-level performance model of the table executor.
 
     python -m stragglar_b200.exec_model stragglar 8 --bytes 1073741824 --blocks 64 [--no-prephase] [--rounds]
+    python -m stragglar_b200.exec_model all 8 --bytes 268435456 --no-prephase      # every algorithm, free and gated
 
 The alpha-beta model of :mod:`.simulate` (the reference's stragglar/simulation.py) prices whole rounds.  This
 module prices what the persistent kernel actually does: every rank's blocks walk the items of the compiled
@@ -339,6 +340,25 @@ def main(argv=None) -> int:
                     help="an item of round r waits until every rank has finished round r-1-LAG (default: no such gate)")
     ap.add_argument("--timeline", type=float, default=0.0, metavar="US", help="print the port use per rank in bins of US")
     args = ap.parse_args(argv)
+    if args.alg == "all":
+        # one line per algorithm: free-running rounds and rounds one after the other
+        params = ModelParams(link_gbs=args.link_gbs, block_gbs=args.block_gbs, flag_us=args.flag_us)
+        print(f"n={args.n}, {args.bytes} bytes per rank; us (fraction of the busiest port's rate)")
+        print(f"{'algorithm':14s} {'blocks':>6s} {'free-running':>16s} {'gated rounds':>16s}")
+        for alg in ("stragglar", "stragglar_a2a", "ring", "rhd", "rsag", "direct"):
+            if alg == "rhd" and args.n & (args.n - 1):
+                continue
+            try:
+                prog = sc.compile_program(alg, args.n, prephase=not args.no_prephase, straggler=args.straggler)
+            except RuntimeError as e:
+                print(f"{alg:14s} not available: {e}")
+                continue
+            blocks = args.blocks or (prog.main.blocks_hint if prog.main.blocks_hint > 0 else 128)
+            floor = prog.link_bytes(args.bytes) / (args.link_gbs * 1e3)
+            free = simulate(prog, args.bytes, blocks, args.tile_bytes, params, round_lag=None if not prog.main.gate_rounds else 10**6)
+            gated = simulate(prog, args.bytes, blocks, args.tile_bytes, params, round_lag=0)
+            print(f"{alg:14s} {blocks:6d} {free.time_us:9.1f} ({floor / free.time_us:.2f}) {gated.time_us:9.1f} ({floor / gated.time_us:.2f})")
+        return 0
     prog = sc.compile_program(args.alg, args.n, prephase=not args.no_prephase, straggler=args.straggler)
     blocks = args.blocks or (prog.main.blocks_hint if prog.main.blocks_hint > 0 else 128)
     delay = None

@@ -226,3 +226,14 @@ def test_simulate_table_with_the_switched_algorithms(capsys):
     assert abs(float(row8["stragglar"]) - (9 * 0.002 + 9 / 7 * 1.39445)) < 2e-3
     a2a, rsag = simulate.compute_costs_switched([4, 8], simulate.LinkModel.b200())
     assert a2a[0] == a2a[1] and rsag[0] < rsag[1]
+
+
+def test_exec_model_cli_compares_all_algorithms(capsys):
+    from stragglar_b200 import exec_model
+    assert exec_model.main(["all", "4", "--bytes", str(8 << 20), "--no-prephase", "--blocks", "8"]) == 0
+    out = capsys.readouterr().out.strip().splitlines()
+    names = [l.split()[0] for l in out[2:]]
+    assert names == ["stragglar", "stragglar_a2a", "ring", "rhd", "rsag", "direct"]
+    assert exec_model.main(["stragglar", "4", "--bytes", str(8 << 20), "--blocks", "8", "--rounds", "--delay-ms", "1"]) == 0
+    text = capsys.readouterr().out
+    assert "straggler held back 1 ms" in text and "round  0:" in text
