@@ -4,7 +4,6 @@ the measured delay taken off, and the fraction of the NVLink roofline.
 
     python bench/summarize.py out/ours.csv out/ref.csv out/nccl.csv
 """
-import csv
 import statistics
 import sys
 from collections import defaultdict

@@ -21,7 +21,7 @@ import argparse
 import re
 import sys
 from collections import Counter, defaultdict
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 _LINE = re.compile(r"Rank (\d+) \| Step (\d+) .*? AR Time: ([\d.]+) ms")

@@ -17,12 +17,12 @@ any rank count (the reference has such code for 4 and 8 GPUs only).
 from __future__ import annotations
 
 import time
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 import torch.distributed as dist
 
-from ..compiler import COPY, F_LOCAL, F_SCALE, PUSH, REDUCE, REDUCE_PUSH, Program, Table
+from ..compiler import COPY, F_LOCAL, F_SCALE, PUSH, REDUCE_PUSH, Program, Table
 
 
 def _chunk_bounds(count: int, esize: int, num_chunks: int) -> List[Tuple[int, int]]:

@@ -24,9 +24,8 @@ StragglAR rounds for n GPUs:
 from __future__ import annotations
 
 import argparse
-import math
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, Iterable, Optional
 
 import numpy as np
 

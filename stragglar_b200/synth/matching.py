@@ -12,7 +12,7 @@ tie-breaks.
 from __future__ import annotations
 
 from functools import lru_cache
-from typing import Dict, Iterable, List, Sequence, Set, Tuple
+from typing import Dict, Sequence, Set, Tuple
 
 Edge = Tuple[int, int, int]  # (u, v, weight)
 

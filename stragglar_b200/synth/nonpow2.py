@@ -23,7 +23,7 @@ from __future__ import annotations
 import math
 import sys
 import time
-from typing import List, Optional, Tuple
+from typing import List, Optional
 
 import numpy as np
 

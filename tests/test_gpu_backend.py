@@ -2,7 +2,6 @@
 rank per device, peer memory over NVLink.  World size 1 runs on any GPU box;
 the multi-rank tests need two or more devices."""
 import os
-import sys
 
 import pytest
 import torch

@@ -1,6 +1,5 @@
 """Analytical model, padding helper and straggler detection."""
 import io
-import math
 from contextlib import redirect_stdout
 
 import pytest
