@@ -175,6 +175,44 @@ def run_reference(args) -> int:
     return 0
 
 
+def experimental_lowerings(world: int, nbytes: int, delay_ms: float, straggler: int = -1) -> dict:
+    """Lowerings that are compiled in but not the default yet, timed by the library's own benchmark program
+    (bin/allreduce: one process, one rank per GPU, device time, max over ranks, every iteration verified) before
+    this process group touches a GPU: round gating for `stragglar`, a 5/8 lane split for `stragglar_a2a`.
+    Informational; a run that fails or takes too long is reported as such and changes nothing else."""
+    exe = os.path.join(ROOT, "bin", "allreduce")
+    if world < 4 or not os.path.exists(exe) or os.environ.get("STRAGGLAR_BENCH_EXPERIMENTS", "1") != "1":
+        return {}
+    out = {}
+    runs = (("stragglar_gated", "stragglar", {"STRAGGLAR_GATE": "1"}),
+            ("stragglar_default_lowering", "stragglar", {}),
+            ("stragglar_a2a_lane1_5of8", "stragglar_a2a", {"STRAGGLAR_LANE1_EIGHTHS": "5"}))
+    for name, alg, env in runs:
+        e = dict(os.environ, STRAGGLAR_NGPUS=str(world), STRAGGLAR_WARMUP="3", **env)
+        if straggler >= 0:
+            e["STRAGGLAR_STRAGGLER"] = str(straggler)
+        for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
+            e.pop(k, None)
+        try:
+            p = subprocess.run([exe, str(nbytes), alg, "8", "-1" if delay_ms <= 0 else f"-1,{delay_ms:g}"],
+                               capture_output=True, text=True, timeout=90, env=e)
+        except subprocess.TimeoutExpired:
+            out[name] = {"error": "timed out after 90 s"}
+            continue
+        rows = [l.split(",") for l in p.stdout.splitlines() if l.startswith(alg + ",")]
+        if p.returncode != 0 or not rows:
+            out[name] = {"error": f"exit {p.returncode}: {(p.stderr or p.stdout).strip()[-160:]!r}"}
+            continue
+        res = {"program": "bin/allreduce", "env": env}
+        for delay in sorted({r[3] for r in rows}):
+            net = [float(r[4]) - float(r[13]) for r in rows if r[3] == delay and len(r) > 13]
+            if net:
+                ms = statistics.median(net)
+                res[f"delay_{delay}"] = {"time_us_net": ms * 1e3, "algbw_GBps": nbytes / 1e9 / (ms / 1e3)}
+        out[name] = res
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -221,6 +259,10 @@ def main() -> int:
     nbytes = count * esize
     straggler = args.straggler if args.straggler >= 0 else world - 1
     delay_ms = args.delay_ms if world > 1 else 0.0
+
+    # rank 0 first times the not-yet-default lowerings with the library's benchmark program (the other ranks wait
+    # in the rendezvous below and have not touched their GPUs yet)
+    experiments = experimental_lowerings(world, nbytes, delay_ms, args.straggler) if rank == 0 and args.alg == "stragglar" else {}
 
     os.environ.setdefault("STRAGGLAR_STAGING_MB", "64")
     os.environ.setdefault("STRAGGLAR_ARENA_MB", str(int(nbytes / (1 << 20)) + 64 + 64))
@@ -362,7 +404,7 @@ def main() -> int:
             "roofline_frac_of_measured": roof_ms / net_ms if net_ms > 0 else None,
             "roofline": ("busiest rank's bytes per direction / 770 GB/s measured peer copy" if world > 1
                          else "read+write of the buffer / 6532.5 GB/s measured copy"),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours", "variants": variants,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours", "variants": variants, "experimental_lowerings": experiments,
         }
         print(json.dumps(out), flush=True)
     dist.destroy_process_group()

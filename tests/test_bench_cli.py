@@ -79,3 +79,36 @@ def test_tune_ranks_settings_with_a_fake_program(tmp_path, monkeypatch, capsys):
     assert ranked[0] == "blocks=128 gate=1" and ranked[1] == "blocks=128"
     assert "path=simta blocks=64 [FAILED: collective failed]" in out
     assert (tmp_path / "raw" / "stragglar_blocks128_gate1.csv").exists()
+
+
+def test_bench_py_times_experimental_lowerings_with_the_benchmark_program(tmp_path, monkeypatch):
+    """bench.py asks bin/allreduce for the lowerings that are not the default yet; a failing run is reported, not fatal."""
+    import importlib.util
+    import stat
+    spec = importlib.util.spec_from_file_location("bench_main", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    (tmp_path / "bin").mkdir()
+    fake = tmp_path / "bin" / "allreduce"
+    fake.write_text("#!/usr/bin/env python3\n"
+                    "import os, sys\n"
+                    "size, alg, iters, delays = int(sys.argv[1]), sys.argv[2], int(sys.argv[3]), sys.argv[4].split(',')\n"
+                    "assert os.environ['STRAGGLAR_NGPUS'] == '8' and 'RANK' not in os.environ\n"
+                    "if os.environ.get('STRAGGLAR_LANE1_EIGHTHS'): sys.stderr.write('collective failed in iteration 0\\n'); sys.exit(2)\n"
+                    "ms = 2.0 if os.environ.get('STRAGGLAR_GATE') == '1' else 2.5\n"
+                    "print('algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s),n,dtype,path,time_us_max,algbw_GBps,busbw_GBps,roofline_frac,real_delay_ms')\n"
+                    "for d in delays:\n"
+                    "    real = max(float(d), 0.0)\n"
+                    "    for i in range(iters):\n"
+                    "        print(f'{alg},{size},{i+1},{float(d):.3f},{ms + real:.3f},1.0,8,float32,tma,0,0,0,0,{real:.3f}')\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setattr(bench, "ROOT", str(tmp_path))
+    monkeypatch.setenv("RANK", "0")
+    out = bench.experimental_lowerings(8, 1 << 30, 5.0)
+    assert abs(out["stragglar_gated"]["delay_-1.000"]["time_us_net"] - 2000.0) < 1e-6
+    assert abs(out["stragglar_gated"]["delay_5.000"]["time_us_net"] - 2000.0) < 1e-6
+    assert abs(out["stragglar_default_lowering"]["delay_-1.000"]["time_us_net"] - 2500.0) < 1e-6
+    assert "collective failed" in out["stragglar_a2a_lane1_5of8"]["error"]
+    assert bench.experimental_lowerings(2, 1 << 30, 5.0) == {}          # nothing to try below four ranks
+    monkeypatch.setenv("STRAGGLAR_BENCH_EXPERIMENTS", "0")
+    assert bench.experimental_lowerings(8, 1 << 30, 5.0) == {}
