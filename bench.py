@@ -195,9 +195,9 @@ def experimental_lowerings(world: int, nbytes: int, delay_ms: float, straggler: 
             e.pop(k, None)
         try:
             p = subprocess.run([exe, str(nbytes), alg, "8", "-1" if delay_ms <= 0 else f"-1,{delay_ms:g}"],
-                               capture_output=True, text=True, timeout=90, env=e)
+                               capture_output=True, text=True, timeout=60, env=e)
         except subprocess.TimeoutExpired:
-            out[name] = {"error": "timed out after 90 s"}
+            out[name] = {"error": "timed out after 60 s"}
             continue
         rows = [l.split(",") for l in p.stdout.splitlines() if l.startswith(alg + ",")]
         if p.returncode != 0 or not rows:
