@@ -28,9 +28,12 @@ def _ext():
 
 
 def configure(**options) -> None:
-    """Options of process groups created afterwards: alg, straggler, path
-    ('tma' | 'simt' | 'simta'), blocks, threads, tile_bytes, timeout_s, arena_bytes,
-    staging_bytes, schedule_text."""
+    """Options of process groups created afterwards: alg ('stragglar' | 'stragglar_a2a' | 'ring' | 'rhd' |
+    'direct' | 'rsag' | 'auto': the straggler-aware variant while a straggler is declared, else rsag or ring by
+    size), straggler (physical rank; -1: the last rank, or nobody for 'auto'), path ('tma' | 'simt' | 'simta'),
+    blocks, threads, tile_bytes, timeout_s, arena_bytes, staging_bytes, schedule_text.  Lowering switches are read
+    from the environment when a program is first built: STRAGGLAR_GATE, STRAGGLAR_COPY, STRAGGLAR_LANES,
+    STRAGGLAR_LANE1_EIGHTHS."""
     _options.update(options)
 
 
