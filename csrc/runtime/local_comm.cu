@@ -241,10 +241,10 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       P.gate_rounds = (sar_table_gate_rounds(t) && count * esize >= sar_gate_min_bytes()) ? 1u : 0u;
       P.lane1_eighths = (uint32_t)sar_table_lane1_eighths(t);
       if (mc_alloc) {
-        for (int g = 0; g < 2; ++g) {
-          if (!mc_alloc->mc[g][r]) continue;
-          P.mc[g].base = (char*)mc_alloc->mc[g][r] + mc_off;
-          P.mc[g].members = mc_alloc->members[g];
+        for (int grp = 0; grp < 2; ++grp) {
+          if (!mc_alloc->mc[grp][r]) continue;
+          P.mc[grp].base = (char*)mc_alloc->mc[grp][r] + mc_off;
+          P.mc[grp].members = mc_alloc->members[grp];
         }
       }
       P.delay_ns = 0;
