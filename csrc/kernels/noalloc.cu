@@ -67,6 +67,14 @@ extern "C" int sar_emulated_allreduce_noalloc(const sar_table* table, void* cons
   const int n = sar_table_nranks(table);
   if (n > SAR_NOALLOC_MAX_RANKS) return fail(err, errlen, 2, "too many ranks for the static scratch array (max 8)");
   if (blocks_per_rank <= 0) blocks_per_rank = 4;
+  {
+    // The parameter and table copies below read host memory that lives only as long as this call;
+    // recorded into a graph they would read it when the graph runs.  Refuse instead.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing((cudaStream_t)stream, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(err, errlen, 1, "not capturable: the stream is being captured; call this entry point outside stream capture");
+  }
   const uint32_t esize = dtype == SAR_F32 ? 4 : 2;
   const uint32_t nch = (uint32_t)sar_table_num_chunks(table);
   for (int r = 0; r < n; ++r) {
@@ -74,7 +82,7 @@ extern "C" int sar_emulated_allreduce_noalloc(const sar_table* table, void* cons
     if (sar_table_num_ops(table, r) > SAR_MAX_OPS || sar_table_num_round_begin(table, r) > 512)
       return fail(err, errlen, 2, "op table too large for the static scratch array");
   }
-  // tiles of at most 1 MiB; the flags of one rank must fit SAR_NOALLOC_MAX_TILES words
+  // tiles of at most 1 MiB; the flags of one rank (all chunks) must fit SAR_NOALLOC_MAX_TILES words
   const uint32_t tile_elems = sar::pick_tile_elems(count, esize, nch, (uint32_t)blocks_per_rank, 2048, 128u << 10);
   SarGeom g = sar::make_geom(count, esize, nch, tile_elems);
   while ((uint64_t)g.tiles_per_chunk * g.num_chunks > SAR_NOALLOC_MAX_TILES) {

@@ -34,14 +34,19 @@ extern "C" {
 // path), but flags, control words, launch parameters and the device copy of
 // the op table live in the static scratch array.
 //
-// Returns 0, or a non-zero code with a message in `err`: 1 = bad argument,
+// Returns 0, or a non-zero code with a message in `err`: 1 = bad argument
+// (this includes a call made while `stream` is being captured, see below),
 // 2 = the request does not fit the scratch array (too many ranks, or a buffer
-// that needs more than SAR_NOALLOC_MAX_TILES tiles of 1 MiB per chunk),
-// other values = a cudaError_t.  It calls no cudaMalloc, cudaFree or
-// allocating library routine.
+// that needs more than SAR_NOALLOC_MAX_TILES tiles of 1 MiB per rank, all
+// chunks together), other values = a cudaError_t.  It calls no cudaMalloc,
+// cudaFree or allocating library routine.
 //
 // The first call on a device looks up the scratch array's device address
 // (cudaGetSymbolAddress); make that first call before any stream capture.
+// The entry point itself must not be called while `stream` is capturing: it
+// copies its launch parameters and the op table from host memory that is only
+// valid during the call, so a captured copy would read freed memory when the
+// graph runs.  Such a call is refused with code 1 and nothing is enqueued.
 // All calls on a device share the array, which keeps the previous call's
 // contents: the words that must start at zero are cleared on `stream` at the
 // start of every call, so calls that overlap on the GPU (different streams,

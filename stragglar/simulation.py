@@ -8,4 +8,4 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from stragglar_b200.simulate import main  # noqa: E402
 
 if __name__ == "__main__":
-    sys.exit(main(sys.argv) if "simulation" != "simulation" else main(sys.argv[1:]))
+    sys.exit(main(sys.argv[1:]))

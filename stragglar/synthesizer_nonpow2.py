@@ -8,4 +8,4 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from stragglar_b200.synth.nonpow2 import main  # noqa: E402
 
 if __name__ == "__main__":
-    sys.exit(main(sys.argv) if "synthesizer_nonpow2" != "simulation" else main(sys.argv[1:]))
+    sys.exit(main(sys.argv))

@@ -82,3 +82,27 @@ def test_requests_beyond_the_static_array_are_refused():
     # misaligned buffer
     ptrs = (C.c_void_p * 2)(xs[0].data_ptr() + 4, xs[1].data_ptr())
     assert f(t2._h, ptrs, 32, 0, 1.0, 1, None, None, err, 256) == 1
+
+
+def test_a_call_during_stream_capture_is_refused():
+    """The entry point copies its parameters from host memory that only lives during the call, so it must not be
+    recorded into a graph: while the stream is capturing it returns code 1 and enqueues nothing."""
+    f = _entry()
+    n = 2
+    table = sc.compile_table("ring", n)
+    xs = [torch.zeros(64, device="cuda:0") for _ in range(n)]
+    ptrs = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+    err = C.create_string_buffer(256)
+    # first call outside capture: resolves the scratch array's address on this device
+    assert f(table._h, ptrs, 64, 0, 1.0, 1, None, torch.cuda.current_stream().cuda_stream, err, 256) == 0
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        g.capture_begin()
+        try:
+            rc = f(table._h, ptrs, 64, 0, 1.0, 1, None, s.cuda_stream, err, 256)
+        finally:
+            g.capture_end()
+    assert rc == 1 and b"not capturable" in err.value
+    torch.cuda.synchronize()
