@@ -253,7 +253,8 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
   const int dt = dtype_code(dtype);
   const uint32_t esize = dt == SAR_F32 ? 4 : 2;
   for (const sar::Compiled& c : prog.phases) {
-    const uint32_t epoch = t.next_epoch(c.channel);   // every rank counts, participant or not
+    const uint64_t epoch64 = t.next_epoch(c.channel);   // every rank counts, participant or not
+    const uint32_t epoch = (uint32_t)epoch64;
     if (!(c.participants >> me & 1)) continue;
     int blocks = t.cuda() ? (opts_.blocks > 0 ? opts_.blocks : sar_cuda_pick_blocks(opts_.path, count * esize)) : 1;
     if (t.cuda() && opts_.blocks <= 0 && c.blocks_hint > 0 && c.blocks_hint < blocks) blocks = c.blocks_hint;
@@ -291,6 +292,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.timeout_ns = (uint64_t)(opts_.timeout_s * 1e9);
       P.status = t.status(); P.trace = reinterpret_cast<uint64_t*>(t.status() + 4); P.delay_ns = 0;
       P.gate_rounds = (c.gate_rounds && count * esize >= sar::gate_min_bytes()) ? 1u : 0u;
+      P.gate_base = epoch64; P.gate_slack = sar::gate_slack();
       P.lane1_eighths = (uint32_t)c.lane1_eighths;
       SAR_CUDA_CHECK(sar_cuda_launch(&P, opts_.path, blocks, opts_.threads, s.stream->stream()));
       ++launches_;
@@ -306,6 +308,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       l.geom = g; l.dtype = (SarDtype)dt; l.scale = scale; l.epoch_base = epoch; l.timeout_s = opts_.timeout_s;
       l.participants = c.participants;
       l.gate_rounds = c.gate_rounds && count * esize >= sar::gate_min_bytes();
+      l.gate_base = epoch64; l.gate_slack = sar::gate_slack();
       l.lane1_eighths = (uint32_t)c.lane1_eighths;
       const uint32_t st = sar::host_run_block(v, rt, l, 0, 1);
       if (st != SAR_OK) {

@@ -75,7 +75,8 @@ class Transport {
   bool check_guards() const;
 
   // next epoch base of a channel (every rank calls this in the same order)
-  uint32_t next_epoch(int channel) { return epoch_[channel] += SAR_VER_STRIDE; }
+  // (64-bit: the low word is the flag epoch, the whole value the base of the round-gate words)
+  uint64_t next_epoch(int channel) { return epoch_[channel] += SAR_VER_STRIDE; }
   uint32_t next_barrier_epoch() { return ++barrier_epoch_; }
 
   // offset into the data region if p lies inside this rank's heap, else -1
@@ -92,7 +93,7 @@ class Transport {
   int device_, rank_, n_;
   size_t data_bytes_, staging_bytes_, total_bytes_;
   char* base_[SAR_MAX_RANKS] = {};
-  uint32_t epoch_[SAR_NUM_CHANNELS] = {};
+  uint64_t epoch_[SAR_NUM_CHANNELS] = {};
   uint32_t barrier_epoch_ = 0;
   std::string shm_name_;
   std::shared_ptr<Heap> heap_;

@@ -18,7 +18,10 @@
 // %globaltimer, so it lasts DELAY ms at any SM clock; extra columns follow the
 // reference's six.  Options come from STRAGGLAR_* environment variables (see
 // bench_common.h).  Each of <NUM_BYTES>, <ALG> and <DELAY> may be a
-// comma-separated list; the matrix then runs in one process.
+// comma-separated list; the matrix then runs in one process.  An ALG entry may carry
+// options of its own, "name:key=value:...", which override the environment for that entry:
+// blocks, stages, tile (bytes), path (run options) and copy, lanes, lane1, gate, slack, gatemin
+// (the STRAGGLAR_COPY / _LANES / _LANE1_EIGHTHS / _GATE / _GATE_SLACK / _GATE_MIN_BYTES lowering switches).
 #include <algorithm>
 #include <cmath>
 
@@ -59,8 +62,44 @@ static void print_round_trace(sar_local_comm* comm, int n, const char* alg, size
   }
 }
 
-static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const std::vector<int>& devs, size_t bytes,
-                      const char* alg, int numIters, float sleepTime, bool header) {
+static std::vector<std::string> split_on(const std::string& s, char sep) {
+  std::vector<std::string> out;
+  std::string cur;
+  for (char ch : s) { if (ch == sep) { out.push_back(cur); cur.clear(); } else cur.push_back(ch); }
+  out.push_back(cur);
+  return out;
+}
+
+// "name:key=value:..." -> name; run options go to `o`, lowering switches to the environment (names returned in `set`)
+static std::string apply_variant(const std::string& label, Options& o, std::vector<std::string>& set) {
+  static const struct { const char* key; const char* env; } kEnv[] = {
+      {"copy", "STRAGGLAR_COPY"}, {"lanes", "STRAGGLAR_LANES"}, {"lane1", "STRAGGLAR_LANE1_EIGHTHS"},
+      {"gate", "STRAGGLAR_GATE"}, {"slack", "STRAGGLAR_GATE_SLACK"}, {"gatemin", "STRAGGLAR_GATE_MIN_BYTES"}};
+  const std::vector<std::string> parts = split_on(label, ':');
+  for (size_t i = 1; i < parts.size(); ++i) {
+    const size_t eq = parts[i].find('=');
+    if (eq == std::string::npos) { fprintf(stderr, "bad option '%s' in %s\n", parts[i].c_str(), label.c_str()); exit(EXIT_FAILURE); }
+    const std::string k = parts[i].substr(0, eq), v = parts[i].substr(eq + 1);
+    if (k == "blocks") o.blocks = atoi(v.c_str());
+    else if (k == "stages") o.stages = atoi(v.c_str());
+    else if (k == "tile") o.tile_bytes = (uint32_t)strtoul(v.c_str(), nullptr, 10);
+    else if (k == "path") o.path = path_from(v.c_str());
+    else {
+      bool known = false;
+      for (const auto& e : kEnv)
+        if (k == e.key) { setenv(e.env, v.c_str(), 1); set.push_back(e.env); known = true; }
+      if (!known) { fprintf(stderr, "unknown option '%s' in %s\n", k.c_str(), label.c_str()); exit(EXIT_FAILURE); }
+    }
+  }
+  return parts[0];
+}
+
+static int run_config(sar_local_comm* comm, Buffers& B, const Options& o_in, const std::vector<int>& devs, size_t bytes,
+                      const char* label, int numIters, float sleepTime, bool header) {
+  Options o = o_in;
+  std::vector<std::string> env_set;
+  const std::string alg_name = apply_variant(label, o, env_set);
+  const char* alg = alg_name.c_str();
   const int n = o.ngpus;
   const uint32_t esize = dtype_size(o.dtype);
   const uint64_t count = bytes / esize;
@@ -106,7 +145,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const 
   std::vector<uint64_t> seeds(n), delay_ns(n, 0);
   if (sleepTime > 0) delay_ns[straggler] = (uint64_t)(sleepTime * 1e6);
   sar_run_opts ro{};
-  ro.path = o.path; ro.blocks = o.blocks; ro.threads = o.threads; ro.tile_bytes = o.tile_bytes;
+  ro.path = o.path; ro.blocks = o.blocks; ro.threads = o.threads; ro.tile_bytes = o.tile_bytes; ro.stages = o.stages;
   ro.timeout_s = o.timeout_s + (sleepTime > 0 ? sleepTime / 1e3 : 0); ro.scale = 1.0f; ro.timed = 1;
   const float atol = o.dtype == SAR_F32 ? 2e-5f : o.dtype == SAR_BF16 ? 0.07f : 0.01f;
   const float rtol = o.dtype == SAR_F32 ? 1e-6f : o.dtype == SAR_BF16 ? 0.02f : 0.004f;
@@ -154,7 +193,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const 
       fprintf(stderr, "collective failed in iteration %d: %s\n", iter, status < 0x1000 ? sar_status_string(status) : cudaGetErrorString((cudaError_t)(status - 0x1000)));
       exit(2);
     }
-    if (ro.trace_rounds) print_round_trace(comm, n, alg, bytes, sleepTime);
+    if (ro.trace_rounds) print_round_trace(comm, n, label, bytes, sleepTime);
     if (o.verify == 2 || (o.verify == 1 && iter == numIters - 1)) {
       for (int r = 0; r < n; ++r) {
         CHECK_CUDA(cudaSetDevice(devs[r]));
@@ -176,7 +215,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const 
         }
         if (res[0]) {
           float worst; memcpy(&worst, &res[1], 4);
-          fprintf(stderr, "VERIFY FAILED: %s %zu B delay %.1f iteration %d rank %d: %u wrong elements (max abs error %g)\n", alg, bytes, sleepTime, iter, r, res[0], worst);
+          fprintf(stderr, "VERIFY FAILED: %s %zu B delay %.1f iteration %d rank %d: %u wrong elements (max abs error %g)\n", label, bytes, sleepTime, iter, r, res[0], worst);
           ++failures;
         }
       }
@@ -190,11 +229,12 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o, const 
     const double algbw = (double)bytes / 1e9 / (net_ms / 1e3);
     const double busbw = algbw * 2.0 * (n - 1) / std::max(n, 1);
     const double roof_ms = link_bytes / (link_gbs * 1e9) * 1e3;
-    printf("%s,%zu,%d,%.3f,%.3f,%.3f,%d,%s,%s,%.1f,%.2f,%.2f,%.3f,%.3f\n", alg, (size_t)count * esize, iter + 1, sleepTime, t, bw, n,
+    printf("%s,%zu,%d,%.3f,%.3f,%.3f,%d,%s,%s,%.1f,%.2f,%.2f,%.3f,%.3f\n", label, (size_t)count * esize, iter + 1, sleepTime, t, bw, n,
            dtype_name(o.dtype), path_label(o.path, B.mc_groups), t * 1e3, algbw, busbw, net_ms > 0 ? roof_ms / net_ms : 0.0, real_delay_ms);
   }
   sar_program_free(prog);
   if (post) sar_program_free(post);
+  for (const std::string& e : env_set) unsetenv(e.c_str());
   return failures;
 }
 
@@ -209,7 +249,7 @@ int main(int argc, char* argv[]) {
   const int numIters = atoi(argv[3]);
   static const char* kAlgs[] = {"ring", "rhd", "direct", "stragglar", "stragglar_a2a", "rsag"};
   for (const auto& a : algs)
-    if (std::none_of(std::begin(kAlgs), std::end(kAlgs), [&](const char* k) { return a == k; })) {
+    if (std::none_of(std::begin(kAlgs), std::end(kAlgs), [&](const char* k) { return a.substr(0, a.find(':')) == k; })) {
       fprintf(stderr, "Invalid algorithm: %s\n", a.c_str());
       exit(EXIT_FAILURE);
     }
@@ -237,7 +277,7 @@ int main(int argc, char* argv[]) {
   for (const auto& s : sizes)
     for (const auto& a : algs)
       for (const auto& d : delays) {
-        if (a == "rhd" && (n & (n - 1))) { fprintf(stderr, "rhd needs a power-of-two GPU count; skipped\n"); continue; }
+        if (a.substr(0, a.find(':')) == "rhd" && (n & (n - 1))) { fprintf(stderr, "rhd needs a power-of-two GPU count; skipped\n"); continue; }
         failures += run_config(comm, B, o, devs, (size_t)strtoull(s.c_str(), NULL, 10), a.c_str(), numIters, (float)atof(d.c_str()), header);
         header = false;
         fflush(stdout);

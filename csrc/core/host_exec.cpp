@@ -2,6 +2,7 @@
 
 #include <chrono>
 #include <cmath>
+#include <cstddef>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -58,6 +59,11 @@ uint64_t gate_min_bytes() {
   return (v && *v) ? strtoull(v, nullptr, 10) : (48ull << 20);
 }
 
+uint32_t gate_slack() {
+  const char* v = getenv("STRAGGLAR_GATE_SLACK");
+  return (v && *v) ? (uint32_t)strtoul(v, nullptr, 10) : 0u;
+}
+
 uint32_t pick_tile_elems(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t blocks, uint32_t min_bytes,
                          uint32_t max_bytes) {
   const uint64_t vw = SAR_VEC_BYTES / esize;
@@ -100,6 +106,17 @@ struct Waiter {
     }
     return true;
   }
+  bool wait64(std::atomic<uint64_t>* w, uint64_t target) const {
+    unsigned spins = 0;
+    while (w->load(std::memory_order_acquire) < target) {
+      if ((++spins & 63) == 0) {
+        if (abort_flag->load(std::memory_order_relaxed)) return false;
+        if (clk::now() > deadline) return false;
+        std::this_thread::yield();
+      }
+    }
+    return true;
+  }
 };
 }  // namespace
 
@@ -108,7 +125,8 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   const int me = v.rank;
   SarCtrl* my_ctrl_raw = reinterpret_cast<SarCtrl*>(v.ctrl[me]);
   (void)my_ctrl_raw;
-  // 0 arrival, 1 exited, 2 abort, 3 blocks_done, 4 rounds_done, 5 round_count (the words of SarCtrl)
+  // 0 arrival, 1 exited, 2 abort, 3 blocks_done, 4 items_done, 5 announced (the words of SarCtrl);
+  // the 64-bit gate words follow at word 32
   auto ctrl_word = [&](int r, int idx) { return v.ctrl[r] + idx; };
   Waiter w{clk::now() + std::chrono::duration_cast<clk::duration>(std::chrono::duration<double>(l.timeout_s + l.delay_ms * 1e-3)),
            ctrl_word(me, 2)};
@@ -127,18 +145,36 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   };
 
   const size_t nrounds = t.round_begin.empty() ? 0 : t.round_begin.size() - 1;
-  // round gating: items this rank has in every schedule round (all lanes); the table's round
-  // list is compact, so the schedule round is taken from the ops
-  uint32_t round_items[SAR_GATE_ALL_DONE + 1] = {};
-  if (l.gate_rounds)
+  // round gating: round_prefix[R] = items this rank has in the schedule rounds before R (all lanes);
+  // the table's round list is compact, so the schedule round is taken from the ops
+  uint32_t round_prefix[SAR_GATE_ALL_DONE + 1] = {};
+  if (l.gate_rounds) {
+    uint32_t items[SAR_GATE_ALL_DONE] = {};
     for (const SarOp& op : t.ops)
-      if (op.round < SAR_GATE_ALL_DONE) round_items[op.round] += sar_op_tiles(g, op);
-  auto next_round_with_items = [&](uint32_t from) -> uint32_t {
-    for (uint32_t rd = from; rd < SAR_GATE_ALL_DONE; ++rd) if (round_items[rd]) return rd;
-    return SAR_GATE_ALL_DONE;
+      if (op.round < SAR_GATE_ALL_DONE) items[op.round] += sar_op_tiles(g, op);
+    for (uint32_t rd = 0; rd < SAR_GATE_ALL_DONE; ++rd) round_prefix[rd + 1] = round_prefix[rd] + items[rd];
+  }
+  auto gate_word = [&](int owner, int about) {
+    return reinterpret_cast<std::atomic<uint64_t>*>(v.ctrl[owner] + offsetof(SarCtrl, gate) / 4) + about;
   };
-  if (l.gate_rounds && block == 0)
-    ctrl_word(me, 4)->store(l.epoch_base + next_round_with_items(0), std::memory_order_release);
+  auto gate_round_for = [&](uint32_t done) -> uint32_t {
+    uint32_t R = 0;
+    while (R < SAR_GATE_ALL_DONE && round_prefix[R + 1] <= done + l.gate_slack) ++R;
+    return R;
+  };
+  // raises this rank's announcement to R in every participant's memory (max: announcements may overtake one another)
+  auto gate_announce = [&](uint32_t R) {
+    uint32_t seen = ctrl_word(me, 5)->load(std::memory_order_relaxed);
+    while (seen < R + 1u && !ctrl_word(me, 5)->compare_exchange_weak(seen, R + 1u, std::memory_order_acq_rel)) {}
+    if (seen >= R + 1u) return;
+    for (int q = 0; q < v.nranks; ++q) {
+      if (!(l.participants >> q & 1)) continue;
+      std::atomic<uint64_t>* gw = gate_word(q, me);
+      uint64_t cur = gw->load(std::memory_order_relaxed);
+      while (cur < l.gate_base + R && !gw->compare_exchange_weak(cur, l.gate_base + R, std::memory_order_acq_rel)) {}
+    }
+  };
+  if (l.gate_rounds && block == 0) gate_announce(gate_round_for(0));
   uint32_t gate_passed = 0;   // schedule rounds up to this one may start
   uint32_t table_lanes = 1;
   for (const SarOp& op : t.ops) if (op.lane) table_lanes = 2;
@@ -171,22 +207,26 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
       const uint32_t tile = t0 + local_tile;
       const uint32_t fidx = sar_flag_index(g, op.chunk, tile);
       bool ok = true;
-      // round gate: every participant has finished the rounds before this one
-      if (l.gate_rounds && op.round > gate_passed) {
-        for (int r = 0; r < v.nranks && ok; ++r)
-          if ((l.participants >> r & 1) && !w.wait(ctrl_word(r, 4), l.epoch_base + op.round)) { give_up(SAR_TIMEOUT_FLAG); ok = false; }
-        if (!ok) break;
-        gate_passed = op.round;
+      // round gate (not for the first round): every participant has announced this round in this rank's memory
+      bool operands_known = false;
+      if (l.gate_rounds && op.round >= 1 && op.round < SAR_GATE_ALL_DONE) {
+        if (op.round > gate_passed) {
+          for (int r = 0; r < v.nranks && ok; ++r)
+            if ((l.participants >> r & 1) && !w.wait64(gate_word(me, r), l.gate_base + op.round)) { give_up(SAR_TIMEOUT_FLAG); ok = false; }
+          if (!ok) break;
+          gate_passed = op.round;
+        }
+        operands_known = l.gate_slack == 0;   // a full barrier: nothing left to wait for
       }
       // wait for the operands
-      for (int q = 0; q < op.nsrc && ok; ++q) {
+      for (int q = 0; q < op.nsrc && ok && !operands_known; ++q) {
         const int src = op.src[q];
         if (!need_arrival(src)) { ok = false; break; }
         if (op.src_ver[q] && !w.wait(v.flags[src] + fidx, l.epoch_base + op.src_ver[q])) { give_up(SAR_TIMEOUT_FLAG); ok = false; }
       }
       const bool reads_local = op.kind == SAR_REDUCE_PUSH || (op.kind == SAR_REDUCE && (op.flags & SAR_F_LOCAL));
       // the own slot must hold the version this op reads or replaces
-      if (ok && op.local_ver && !w.wait(v.flags[me] + fidx, l.epoch_base + op.local_ver)) {
+      if (ok && !operands_known && op.local_ver && !w.wait(v.flags[me] + fidx, l.epoch_base + op.local_ver)) {
         give_up(SAR_TIMEOUT_FLAG); ok = false;
       }
       if (!ok) break;
@@ -215,9 +255,9 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
         for (int q = 0; q < op.nsrc; ++q)
           v.flags[op.src[q]][fidx].store(l.epoch_base + op.push_ver, std::memory_order_release);
       // round gate: whoever finishes the rank's last item of the round announces the next round
-      if (l.gate_rounds && ctrl_word(me, 5)->fetch_add(1, std::memory_order_acq_rel) + 1 == round_items[op.round]) {
-        ctrl_word(me, 5)->store(0, std::memory_order_relaxed);
-        ctrl_word(me, 4)->store(l.epoch_base + next_round_with_items(op.round + 1u), std::memory_order_release);
+      if (l.gate_rounds && op.round < SAR_GATE_ALL_DONE) {
+        const uint32_t R = gate_round_for(ctrl_word(me, 4)->fetch_add(1, std::memory_order_acq_rel) + 1);
+        if (R) gate_announce(R);
       }
     }
     item_base += items;
@@ -227,7 +267,8 @@ uint32_t host_run_block(const HostRankView& v, const RankTable& t, const HostLau
   uint32_t done = ctrl_word(me, 3)->fetch_add(1, std::memory_order_acq_rel) + 1;
   if (done == (uint32_t)nblocks_all) {
     ctrl_word(me, 3)->store(0, std::memory_order_relaxed);
-    ctrl_word(me, 5)->store(0, std::memory_order_relaxed);   // a run that gave up may have left a partial count
+    ctrl_word(me, 4)->store(0, std::memory_order_relaxed);
+    ctrl_word(me, 5)->store(0, std::memory_order_relaxed);
     if (status == SAR_OK && !ctrl_word(me, 2)->load(std::memory_order_relaxed)) {
       ctrl_word(me, 1)->store(l.epoch_base, std::memory_order_release);
       for (int r = 0; r < v.nranks; ++r)
@@ -247,8 +288,8 @@ struct HostArena {
     for (int r = 0; r < n; ++r) {
       flags[r].reset(new std::atomic<uint32_t>[nflags]);
       for (size_t i = 0; i < nflags; ++i) flags[r][i].store(0, std::memory_order_relaxed);
-      ctrl[r].reset(new std::atomic<uint32_t>[32 * SAR_NUM_CHANNELS]);
-      for (int i = 0; i < 32 * SAR_NUM_CHANNELS; ++i) ctrl[r][i].store(0, std::memory_order_relaxed);
+      ctrl[r].reset(new std::atomic<uint32_t>[SAR_CTRL_WORDS * SAR_NUM_CHANNELS]);
+      for (int i = 0; i < (int)(SAR_CTRL_WORDS * SAR_NUM_CHANNELS); ++i) ctrl[r][i].store(0, std::memory_order_relaxed);
     }
   }
 };
@@ -285,13 +326,15 @@ static uint32_t run_phases(const std::vector<const Compiled*>& phases, void* con
               for (int q = 0; q < n; ++q) {
                 v.buf[q] = bufs[q];
                 v.flags[q] = arena.flags[q].get() + (size_t)c.channel * SAR_FLAG_CAPACITY;
-                v.ctrl[q] = arena.ctrl[q].get() + 32 * c.channel;
+                v.ctrl[q] = arena.ctrl[q].get() + SAR_CTRL_WORDS * c.channel;
               }
               HostLaunch l;
               uint32_t te = tile_elems ? tile_elems : pick_tile_elems(count, esize, c.num_chunks, blocks, 256, 1 << 16);
               l.geom = make_geom(count, esize, c.num_chunks, te);
               l.dtype = dtype; l.scale = scale; l.timeout_s = timeout_s; l.participants = c.participants;
               l.gate_rounds = c.gate_rounds;
+              l.gate_slack = gate_slack();
+              l.gate_base = (uint64_t)(rep + 1) * SAR_VER_STRIDE;
               l.lane1_eighths = (uint32_t)c.lane1_eighths;
               l.epoch_base = (uint32_t)(rep + 1) * SAR_VER_STRIDE;
               l.delay_ms = (!delayed && delay_ms) ? delay_ms[r] : 0.0;

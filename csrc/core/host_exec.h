@@ -31,6 +31,8 @@ struct HostLaunch {
   double delay_ms = 0.0;                  // sleep before arriving (an injected straggler delay)
   uint32_t participants = 0;              // ranks that run this collective (exit barrier set)
   bool gate_rounds = false;               // rounds one after the other (every rank of the launch must agree)
+  uint32_t gate_slack = 0;                // items of a round that may still run when the next round opens (0: full barrier)
+  uint64_t gate_base = SAR_VER_STRIDE;    // stands for round 0 of this launch; grows with epoch_base and never wraps
   uint32_t lane1_eighths = 4;             // share of the blocks of lane 1 (see sar_lane_of_block)
 };
 
@@ -52,6 +54,8 @@ uint32_t host_execute_program(const Program& p, void* const* bufs, uint64_t coun
 // (STRAGGLAR_GATE_MIN_BYTES, default 48 MiB: in the tile-level model of an 8-GPU box the gated rounds win
 // from 64 MiB up and lose at 32 MiB).  Every rank of a launch sees the same size, hence the same answer.
 uint64_t gate_min_bytes();
+// STRAGGLAR_GATE_SLACK (default 0, see SAR_GATE_ALL_DONE in table.h); every rank must see the same value.
+uint32_t gate_slack();
 
 uint32_t pick_tile_elems(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t blocks, uint32_t min_bytes,
                          uint32_t max_bytes);

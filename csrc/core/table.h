@@ -92,21 +92,32 @@ struct SarCtrl {
   uint32_t exited;     // epoch_base of the newest collective this rank has left
   uint32_t abort_flag; // set by any block that timed out; makes the others return
   uint32_t blocks_done;// local counter to find the last block of a launch
-  // round gating (see SAR_GATE_ALL_DONE): epoch_base + the first schedule round this rank has not
-  // finished yet (read by peers), and a local counter of the items finished in the current round
-  uint32_t rounds_done;
-  uint32_t round_count;
+  // round gating (local words, reset by the last block of a launch): items this rank has finished in
+  // the launch, and the newest round it has announced to its peers
+  uint32_t items_done;
+  uint32_t announced;
   uint32_t reserved[26];
+  // round gating: gate[q] is written by rank q into THIS rank's memory (so that waiting for a round
+  // polls local memory only) and holds gate_base + R once rank q has finished its items of every
+  // round before R.  64-bit and raised with a max-reduction: announcements of different rounds may
+  // overtake one another on the way, and the value never wraps.
+  uint64_t gate[SAR_MAX_RANKS];
 };
-static_assert(sizeof(SarCtrl) == 128, "SarCtrl layout");
+static_assert(sizeof(SarCtrl) == 256, "SarCtrl layout");
+#define SAR_CTRL_WORDS (sizeof(SarCtrl) / 4)
 // Round gating.  The rounds of a matching-based schedule are contention-free one at a time: in
 // every round a rank sends at most one chunk and receives at most one.  When the rounds overlap
 // freely, a rank that holds a finished chunk serves the readers of several rounds at once, each
 // at a fraction of the link rate, and what depends on them is late.  With gating, an item of
-// round r starts only when every participant has finished its items of all rounds before r
-// (`rounds_done` >= epoch_base + r); a rank without items in a round skips it when it
-// announces.  Tiles still pipeline inside a round.  SAR_GATE_ALL_DONE is announced after the
-// last round; it bounds the number of rounds a gated table may have (< SAR_VER_STRIDE).
+// round r >= 1 starts only when every participant has announced r, i.e. has finished its items of
+// all rounds before r (a rank without items in a round skips it when it announces).  The first
+// round is not gated: a pre-phase among the early ranks must not wait for a late rank's arrival.
+// With `gate_slack` = 0 the gate is a full barrier between rounds, every operand of a gated item is
+// known to be complete, and the item skips its flag waits (no polling of peer memory at all);
+// with a slack of s items a rank announces a round when all but s of the items before it are
+// done, the tail of a round overlaps the head of the next, and items wait for their flags as
+// usual.  Tiles still pipeline inside a round.  SAR_GATE_ALL_DONE is announced after the last
+// round; it bounds the number of rounds a gated table may have (< SAR_VER_STRIDE).
 #define SAR_GATE_ALL_DONE 31u
 
 // Chunk geometry for `count` elements of `esize` bytes in `num_chunks` chunks.

@@ -215,7 +215,9 @@ struct TableGeom {
   RoundGeom round[2][SAR_MAX_ROUNDS];   // per lane
   uint32_t num_rounds;
   uint32_t lanes;                       // lanes in effect for this launch (1 or 2)
-  uint32_t round_items[SAR_GATE_ALL_DONE + 1];   // round gating: this rank's items per schedule round (all lanes)
+  // round gating: round_prefix[R] = this rank's items in the schedule rounds before R (all lanes);
+  // round_prefix[SAR_GATE_ALL_DONE] is the total
+  uint32_t round_prefix[SAR_GATE_ALL_DONE + 1];
 };
 
 // All threads of the block; ends with a block barrier.
@@ -233,11 +235,14 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t n
     G.op[o].tile0 = t0;
   }
   if (threadIdx.x == 0 && P.gate_rounds) {
-    for (uint32_t r = 0; r <= SAR_GATE_ALL_DONE; ++r) G.round_items[r] = 0;
+    uint32_t items[SAR_GATE_ALL_DONE];
+    for (uint32_t r = 0; r < SAR_GATE_ALL_DONE; ++r) items[r] = 0;
     for (uint32_t o = 0; o < nops && o < SAR_MAX_OPS; ++o) {
       const SarOp op = P.ops[o];
-      if (op.round < SAR_GATE_ALL_DONE) G.round_items[op.round] += sar_op_tiles(P.geom, op);
+      if (op.round < SAR_GATE_ALL_DONE) items[op.round] += sar_op_tiles(P.geom, op);
     }
+    G.round_prefix[0] = 0;
+    for (uint32_t r = 0; r < SAR_GATE_ALL_DONE; ++r) G.round_prefix[r + 1] = G.round_prefix[r] + items[r];
   }
   if (threadIdx.x == 0) {
     uint32_t table_lanes = 1;
@@ -316,11 +321,11 @@ __device__ __forceinline__ bool op_reads_local(const SarOp* op) {
   return op->kind == SAR_REDUCE_PUSH || (op->kind == SAR_REDUCE && (op->flags & SAR_F_LOCAL));
 }
 
-// Per-round statistics (optional): when the first item of a round started, how long the items
-// of the round waited for their operands, when the last one was announced.
+// Per-round statistics (optional): when the first item of a round had its operands and could start,
+// how long the items of the round waited for their operands, when the last one was announced.
 __device__ __forceinline__ void trace_item_start(const SarLaunchParams& P, const SarOp* op, uint64_t t_begin, uint64_t t_ready) {
   if (!P.trace_rounds || op->round >= SAR_MAX_ROUNDS) return;
-  atomicMin((unsigned long long*)&P.trace[2 + op->round], (unsigned long long)t_begin);
+  atomicMin((unsigned long long*)&P.trace[2 + op->round], (unsigned long long)t_ready);
   atomicAdd((unsigned long long*)&P.trace[2 + 2 * SAR_MAX_ROUNDS + op->round], (unsigned long long)(t_ready - t_begin));
 }
 __device__ __forceinline__ void trace_item_end(const SarLaunchParams& P, const SarOp* op) {
@@ -329,24 +334,61 @@ __device__ __forceinline__ void trace_item_end(const SarLaunchParams& P, const S
 }
 
 // ---- round gating (see SAR_GATE_ALL_DONE in table.h)
-__device__ __forceinline__ uint32_t next_round_with_items(const TableGeom& G, uint32_t from) {
-  for (uint32_t r = from; r < SAR_GATE_ALL_DONE; ++r) if (G.round_items[r]) return r;
-  return SAR_GATE_ALL_DONE;
+__device__ __forceinline__ uint64_t ld_relaxed_sys_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
 }
-// One thread of the rank's block 0, after resolve_table: the first round this rank has items in.
+__device__ __forceinline__ void red_max_sys_u64(uint64_t* p, uint64_t v) {
+  asm volatile("red.relaxed.sys.global.max.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// The newest round this rank may announce once `done` of its items are finished: the largest R such
+// that all but `slack` of its items of the rounds before R are done (rounds without items are skipped).
+__device__ __forceinline__ uint32_t gate_round_for(const TableGeom& G, uint32_t done, uint32_t slack) {
+  uint32_t R = 0;
+  while (R < SAR_GATE_ALL_DONE && G.round_prefix[R + 1] <= done + slack) ++R;
+  return R;
+}
+// Raises this rank's announcement to R in every participant's memory (its own included).  The caller has
+// ordered the data of the finished items before this call (fence at system scope).
+__device__ __forceinline__ void gate_announce(const SarLaunchParams& P, uint32_t R) {
+  SarCtrl* me = P.comm.ctrl[P.rank];
+  if (atomicMax(&me->announced, R + 1u) >= R + 1u) return;   // somebody has announced R (or more) already
+  for (int q = 0; q < P.nranks; ++q)
+    if (P.participants >> q & 1) red_max_sys_u64(&P.comm.ctrl[q]->gate[P.rank], P.gate_base + R);
+}
+// One thread of the rank's block 0, after resolve_table: the rounds before the first one with items are done.
 __device__ __forceinline__ void gate_announce_first(const SarLaunchParams& P, const TableGeom& G) {
-  st_release_sys(&P.comm.ctrl[P.rank]->rounds_done, P.epoch_base + next_round_with_items(G, 0));
+  fence_sys();
+  gate_announce(P, gate_round_for(G, 0, 0));
 }
-// The thread that has just announced an item: counts it, and announces the rank's next round when
-// it was the last item of the current one.  (With gating all items in flight on a rank belong to
-// one round, so one counter serves all rounds.)
+// The thread that has just announced an item: counts it, and announces the rounds that this completes.
 __device__ __forceinline__ void gate_item_done(const SarLaunchParams& P, const TableGeom& G, const SarOp* op) {
   if (!P.gate_rounds || op->round >= SAR_GATE_ALL_DONE) return;
   SarCtrl* me = P.comm.ctrl[P.rank];
-  if (atomicAdd(&me->round_count, 1u) + 1u != G.round_items[op->round]) return;
-  atomicExch(&me->round_count, 0u);
-  fence_sys();
-  st_relaxed_sys(&me->rounds_done, P.epoch_base + next_round_with_items(G, op->round + 1u));
+  const uint32_t done = atomicAdd(&me->items_done, 1u) + 1u;
+  const uint32_t R = gate_round_for(G, done, P.gate_slack);
+  if (R == 0 || *(volatile uint32_t*)&me->announced >= R + 1u) return;
+  fence_sys();   // the items counted so far (by any thread of this rank) are visible before the announcement
+  gate_announce(P, R);
+}
+// Bounded wait until every participant has announced round `round` (the words are in this rank's memory).
+__device__ __noinline__ bool wait_gate(const SarLaunchParams& P, uint32_t round, const WaitCtx& w) {
+  const uint64_t target = P.gate_base + round;
+  const uint64_t* g = P.comm.ctrl[P.rank]->gate;
+  uint32_t ns = 20;
+  for (uint64_t it = 0;; ++it) {
+    bool all = true;
+    for (int r = 0; r < P.nranks; ++r)
+      if ((P.participants >> r & 1) && ld_relaxed_sys_u64(g + r) < target) all = false;
+    if (all) { fence_sys(); return true; }   // acquire: what the announcers ordered before is visible now
+    if ((it & 15) == 15) {
+      if (*(volatile uint32_t*)w.abort_flag) return false;
+      if (globaltimer() > w.deadline) { record_failure(w, SAR_TIMEOUT_FLAG); return false; }
+    }
+    __nanosleep(ns);
+    if (ns < 200) ns += ns >> 1;
+  }
 }
 
 // Waits (one thread) until every operand of the item is ready.  `gate_passed`: the newest schedule
@@ -354,11 +396,13 @@ __device__ __forceinline__ void gate_item_done(const SarLaunchParams& P, const T
 __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const WaitCtx& w, uint32_t* arrived_mask,
                                 uint32_t* gate_passed) {
   const SarOp* op = it.op;
-  if (P.gate_rounds && op->round > *gate_passed && op->round < SAR_GATE_ALL_DONE) {
-    for (int r = 0; r < P.nranks; ++r)
-      if ((P.participants >> r & 1) && !wait_word(&P.comm.ctrl[r]->rounds_done, P.epoch_base + op->round, w, SAR_TIMEOUT_FLAG))
-        return false;
-    *gate_passed = op->round;
+  if (P.gate_rounds && op->round >= 1 && op->round < SAR_GATE_ALL_DONE) {
+    if (op->round > *gate_passed) {
+      if (!wait_gate(P, op->round, w)) return false;
+      *gate_passed = op->round;
+    }
+    // a full barrier between rounds: every participant has arrived and every operand is complete
+    if (P.gate_slack == 0) { *arrived_mask = P.participants; return true; }
   }
   for (int q = 0; q < op->nsrc; ++q) {
     const int src = op->src[q];
@@ -614,7 +658,8 @@ __device__ void leave_collective(const SarLaunchParams& P, const WaitCtx& w, uin
   const uint32_t done = atomicAdd(&me->blocks_done, 1u) + 1u;
   if (done != nblocks) return;
   me->blocks_done = 0;
-  me->round_count = 0;   // a launch that gave up may have left a partial count
+  me->items_done = 0;
+  me->announced = 0;
   __threadfence();
   if (*(volatile uint32_t*)w.abort_flag == 0) {
     fence_sys();
@@ -790,6 +835,8 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
   constexpr int N = Vec<T>::N;
   const uint32_t tid = threadIdx.x;
   const uint32_t warp = tid >> 5, lane = tid & 31;
+  // ring stages in use: fewer stages keep fewer bytes in flight per block
+  const uint32_t nst = (P.stages >= 2 && P.stages < (uint32_t)kStages) ? P.stages : (uint32_t)kStages;
   WaitCtx w = enter_collective(P, block);
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
@@ -812,7 +859,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       Item it;
       auto acquire_stage = [&](uint32_t s) -> bool {
         // the first pass over the ring finds every stage free
-        if (seq >= (uint32_t)kStages) return mbar_wait(&S.empty[s], ((seq / kStages) - 1) & 1, w);
+        if (seq >= nst) return mbar_wait(&S.empty[s], ((seq / nst) - 1) & 1, w);
         return true;
       };
       while (ok && walk.next(&it)) {
@@ -831,7 +878,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         uint32_t done = 0;
         do {
           const uint32_t bytes = vec_bytes - done < slot_bytes ? vec_bytes - done : slot_bytes;
-          const uint32_t s = seq % kStages;
+          const uint32_t s = seq % nst;
           if (!acquire_stage(s)) { ok = false; break; }
           StageDesc& d = S.desc[s];
           d.op = op; d.byte_off = it.elem0 * sizeof(T) + done; d.bytes = bytes; d.slot_bytes = slot_bytes;
@@ -854,11 +901,11 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       }
       // end marker (also after a failure, so that the consumers stop)
       {
-        const uint32_t s = seq % kStages;
+        const uint32_t s = seq % nst;
         bool got = true;
-        if (seq >= (uint32_t)kStages) {
+        if (seq >= nst) {
           // on the failure path the deadline has usually passed: take the stage only if it is free already
-          got = ok ? mbar_wait(&S.empty[s], ((seq / kStages) - 1) & 1, w) : mbar_try_wait(&S.empty[s], ((seq / kStages) - 1) & 1);
+          got = ok ? mbar_wait(&S.empty[s], ((seq / nst) - 1) & 1, w) : mbar_try_wait(&S.empty[s], ((seq / nst) - 1) & 1);
         }
         if (got) { S.desc[s].op = nullptr; mbar_arrive(&S.full[s]); }
         else *(volatile int*)&S.abort_seen = 1;
@@ -872,10 +919,10 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
     uint32_t seq = 0;
     uint32_t landed = 0, pend_tail = 0;             // private copies of the storing thread (ctid 0)
     while (true) {
-      const uint32_t s = seq % kStages;
+      const uint32_t s = seq % nst;
       bool ok = true;
       if (lane == 0) {
-        if (ctid == 0 && landed < seq && !mbar_try_wait(&S.full[s], (seq / kStages) & 1)) {
+        if (ctid == 0 && landed < seq && !mbar_try_wait(&S.full[s], (seq / nst) & 1)) {
           // The pipeline has run dry, perhaps because the producer waits for a tile
           // that (through other ranks) depends on an item whose stores have not been
           // reported as landed yet: report everything now.
@@ -883,7 +930,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
           landed = seq;
           st_release_cta(&S.landed, landed);
         }
-        ok = mbar_wait(&S.full[s], (seq / kStages) & 1, w);
+        ok = mbar_wait(&S.full[s], (seq / nst) & 1, w);
         if (*(volatile int*)&S.abort_seen) ok = false;
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -961,7 +1008,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         }
         // the previous piece's stores have read their stage: hand it back
         bulk_wait_read<1>();
-        if (seq >= 1) mbar_arrive(&S.empty[(seq - 1) % kStages]);
+        if (seq >= 1) mbar_arrive(&S.empty[(seq - 1) % nst]);
         // at most three store groups stay in flight; older ones have landed
         bulk_wait_all<3>();
         if (seq >= 3 && landed < seq - 2) { landed = seq - 2; st_release_cta(&S.landed, landed); }
@@ -1008,9 +1055,9 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
   if (tid == 0 && *(volatile uint32_t*)w.abort_flag) {
     const uint32_t issued = S.issued;
     const uint64_t limit = globaltimer() + 2000000ull;
-    for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+    for (uint32_t s = 0; s < nst; ++s) {
       if (issued <= s) continue;
-      const uint32_t use = (issued - 1 - s) / kStages;   // newest use of stage s
+      const uint32_t use = (issued - 1 - s) / nst;   // newest use of stage s
       while (!mbar_try_wait(&S.full[s], use & 1) && globaltimer() < limit) {}
     }
   }

@@ -38,6 +38,9 @@ struct SarLaunchParams {
   uint32_t trace_rounds;  // != 0: trace holds SAR_TRACE_WORDS words and the per-round statistics are kept
   uint32_t gate_rounds;   // != 0: the rounds run one after the other (every rank of the launch agrees; see table.h)
   uint32_t lane1_eighths; // share of the blocks of lane 1, in eighths (0 or 4: half; see sar_lane_of_block)
+  uint32_t gate_slack;    // round gating: items of a round that may still be running when the next round opens
+  uint64_t gate_base;     // round gating: value that stands for round 0 of this launch (grows by >= 32 per launch)
+  uint32_t stages;        // bulk-copy path: ring stages in use (0 or > the ring size: all)
   uint32_t pad1;
   uint64_t delay_ns;      // spin this long before arriving (a late rank when ranks share one launch)
   SarMcGroup mc[2];       // multicast views (simt path): all ranks, and e.g. the non-stragglers

@@ -32,7 +32,7 @@ struct sar_local_comm {
   int n = 0;
   bool emulate = false;
   std::vector<Rank> ranks;
-  uint32_t epoch[SAR_NUM_CHANNELS] = {};
+  uint64_t epoch[SAR_NUM_CHANNELS] = {};   // 64-bit: the low word is the flag epoch, the whole value the gate base
   SarLaunchParams* d_params = nullptr;   // emulate: n entries on devices[0]
   std::vector<sar::SymmAlloc*> allocs;   // symmetric buffers handed out by sar_local_alloc
 };
@@ -235,10 +235,12 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       if (!dt) return 1;
       P.ops = dt->ops; P.round_begin = dt->round_begin; P.num_rounds = dt->num_rounds;
       P.geom = g; P.rank = r; P.nranks = n; P.participants = parts;
-      P.epoch_base = c->epoch[ch]; P.scale = o->scale; P.dtype = dtype;
+      P.epoch_base = (uint32_t)c->epoch[ch]; P.gate_base = c->epoch[ch]; P.scale = o->scale; P.dtype = dtype;
       P.timeout_ns = (uint64_t)(timeout_s * 1e9);
       P.status = rk.status; P.trace = rk.trace; P.trace_rounds = o->trace_rounds ? 1u : 0u;
       P.gate_rounds = (sar_table_gate_rounds(t) && count * esize >= sar_gate_min_bytes()) ? 1u : 0u;
+      P.gate_slack = sar::gate_slack();
+      P.stages = o->stages > 0 ? (uint32_t)o->stages : 0u;
       P.lane1_eighths = (uint32_t)sar_table_lane1_eighths(t);
       if (mc_alloc) {
         for (int grp = 0; grp < 2; ++grp) {
@@ -288,7 +290,7 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
   uint32_t barrier_epoch = 0;
   SarCtrl* bctrl[SAR_MAX_RANKS] = {};
   if (o->timed) {
-    barrier_epoch = ++c->epoch[SAR_NUM_CHANNELS - 1];
+    barrier_epoch = (uint32_t)++c->epoch[SAR_NUM_CHANNELS - 1];
     for (int r = 0; r < n; ++r) bctrl[r] = c->ranks[r].ctrl + (SAR_NUM_CHANNELS - 1);
   }
   for (int r = 0; r < n; ++r) {

@@ -24,6 +24,7 @@ struct sar_run_opts {
   float scale;            // fused multiplier of the result
   int timed;              // 1: bracket every rank's work with events after a device-side start barrier
   int trace_rounds;       // 1: keep per-round statistics of this run (see sar_local_round_trace)
+  int stages;             // bulk-copy path: shared-memory ring stages per block (<= 0: all six)
 };
 
 // devices[r] is the CUDA device of rank r.  emulate != 0 places every rank on

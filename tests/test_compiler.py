@@ -231,7 +231,11 @@ def test_round_gating_attribute_and_host_execution(monkeypatch):
     assert not sc.compile_program("stragglar", 2).main.gate_rounds       # one round: nothing to gate
     assert not sc.compile_program("ring", 8).main.gate_rounds            # "1" gates the synthesized schedule only
     monkeypatch.setenv("STRAGGLAR_GATE", "all")
-    for alg, n in (("stragglar", 8), ("stragglar", 6), ("stragglar_a2a", 4), ("ring", 4), ("rhd", 8), ("direct", 4), ("rsag", 4)):
+    for alg, n, slack in (("stragglar", 8, 0), ("stragglar", 8, 5), ("stragglar", 6, 0), ("stragglar_a2a", 4, 2), ("ring", 4, 0),
+                          ("rhd", 8, 0), ("direct", 4, 0), ("rsag", 4, 3)):
+        # slack 0: a full barrier between rounds, gated items skip their flag waits; slack s: a round opens when
+        # all but s items before it are done and items wait for their flags as usual
+        monkeypatch.setenv("STRAGGLAR_GATE_SLACK", str(slack))
         prog = sc.compile_program(alg, n)
         assert prog.main.gate_rounds, alg
         bufs = seeded_inputs(n, 20_011)
