@@ -259,7 +259,9 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
     int blocks = t.cuda() ? (opts_.blocks > 0 ? opts_.blocks : sar_cuda_pick_blocks(opts_.path, count * esize)) : 1;
     if (t.cuda() && opts_.blocks <= 0 && c.blocks_hint > 0 && c.blocks_hint < blocks) blocks = c.blocks_hint;
     if (t.cuda() && opts_.blocks <= 0 && n == 1 && blocks == 128) blocks = 148;   // a lone rank: one block per SM
-    const uint32_t tile_max = opts_.tile_bytes ? opts_.tile_bytes : (t.cuda() ? sar_cuda_default_tile_bytes(opts_.path) : (128u << 10));
+    const bool gated = c.gate_rounds && count * esize >= sar::gate_min_bytes();
+    const uint32_t tile_max = opts_.tile_bytes ? opts_.tile_bytes
+                            : (t.cuda() ? (gated ? sar::gate_tile_bytes() : sar_cuda_default_tile_bytes(opts_.path)) : (128u << 10));
     const uint32_t tile_elems = sar::pick_tile_elems(count, esize, (uint32_t)c.num_chunks, (uint32_t)blocks, 2048, tile_max);
     const SarGeom g = sar::make_geom(count, esize, (uint32_t)c.num_chunks, tile_elems);
     TORCH_CHECK((uint64_t)g.tiles_per_chunk * g.num_chunks <= SAR_FLAG_CAPACITY, "tensor too large for the flag array");
@@ -291,8 +293,9 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.epoch_base = epoch; P.scale = scale; P.dtype = dt;
       P.timeout_ns = (uint64_t)(opts_.timeout_s * 1e9);
       P.status = t.status(); P.trace = reinterpret_cast<uint64_t*>(t.status() + 4); P.delay_ns = 0;
-      P.gate_rounds = (c.gate_rounds && count * esize >= sar::gate_min_bytes()) ? 1u : 0u;
-      P.gate_base = epoch64; P.gate_slack = sar::gate_slack();
+      P.gate_rounds = gated ? 1u : 0u;
+      P.gate_base = epoch64; P.gate_slack = sar::gate_slack(g.tiles_per_chunk);
+      P.stages = (uint32_t)c.stages_hint;
       P.lane1_eighths = (uint32_t)c.lane1_eighths;
       SAR_CUDA_CHECK(sar_cuda_launch(&P, opts_.path, blocks, opts_.threads, s.stream->stream()));
       ++launches_;
@@ -307,8 +310,8 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       sar::HostLaunch l;
       l.geom = g; l.dtype = (SarDtype)dt; l.scale = scale; l.epoch_base = epoch; l.timeout_s = opts_.timeout_s;
       l.participants = c.participants;
-      l.gate_rounds = c.gate_rounds && count * esize >= sar::gate_min_bytes();
-      l.gate_base = epoch64; l.gate_slack = sar::gate_slack();
+      l.gate_rounds = gated;
+      l.gate_base = epoch64; l.gate_slack = sar::gate_slack(g.tiles_per_chunk);
       l.lane1_eighths = (uint32_t)c.lane1_eighths;
       const uint32_t st = sar::host_run_block(v, rt, l, 0, 1);
       if (st != SAR_OK) {

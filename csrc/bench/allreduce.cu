@@ -20,7 +20,7 @@
 // bench_common.h).  Each of <NUM_BYTES>, <ALG> and <DELAY> may be a
 // comma-separated list; the matrix then runs in one process.  An ALG entry may carry
 // options of its own, "name:key=value:...", which override the environment for that entry:
-// blocks, stages, tile (bytes), path (run options) and copy, lanes, lane1, gate, slack, gatemin
+// blocks, stages, win (store groups in flight), tile (bytes), path (run options) and copy, lanes, lane1, gate, slack, gatemin
 // (the STRAGGLAR_COPY / _LANES / _LANE1_EIGHTHS / _GATE / _GATE_SLACK / _GATE_MIN_BYTES lowering switches).
 #include <algorithm>
 #include <cmath>
@@ -82,6 +82,7 @@ static std::string apply_variant(const std::string& label, Options& o, std::vect
     const std::string k = parts[i].substr(0, eq), v = parts[i].substr(eq + 1);
     if (k == "blocks") o.blocks = atoi(v.c_str());
     else if (k == "stages") o.stages = atoi(v.c_str());
+    else if (k == "win") o.store_window = atoi(v.c_str());
     else if (k == "tile") o.tile_bytes = (uint32_t)strtoul(v.c_str(), nullptr, 10);
     else if (k == "path") o.path = path_from(v.c_str());
     else {
@@ -145,7 +146,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o_in, con
   std::vector<uint64_t> seeds(n), delay_ns(n, 0);
   if (sleepTime > 0) delay_ns[straggler] = (uint64_t)(sleepTime * 1e6);
   sar_run_opts ro{};
-  ro.path = o.path; ro.blocks = o.blocks; ro.threads = o.threads; ro.tile_bytes = o.tile_bytes; ro.stages = o.stages;
+  ro.path = o.path; ro.blocks = o.blocks; ro.threads = o.threads; ro.tile_bytes = o.tile_bytes; ro.stages = o.stages; ro.store_window = o.store_window;
   ro.timeout_s = o.timeout_s + (sleepTime > 0 ? sleepTime / 1e3 : 0); ro.scale = 1.0f; ro.timed = 1;
   const float atol = o.dtype == SAR_F32 ? 2e-5f : o.dtype == SAR_BF16 ? 0.07f : 0.01f;
   const float rtol = o.dtype == SAR_F32 ? 1e-6f : o.dtype == SAR_BF16 ? 0.02f : 0.004f;

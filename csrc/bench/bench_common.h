@@ -40,6 +40,7 @@ struct Options {
   int straggler = -1;      // STRAGGLAR_STRAGGLER: physical rank that is late (default n-1)
   int path = SAR_PATH_SIMT;// STRAGGLAR_PATH = simt | tma | simta
   int blocks = 0, threads = 0;
+  int store_window = 0;    // STRAGGLAR_STORE_WINDOW: store groups a block keeps in flight on the bulk-copy path (3, 8, 16)
   int stages = 0;          // STRAGGLAR_STAGES: ring stages per block on the bulk-copy path (0: all)
   uint32_t tile_bytes = 0;
   double timeout_s = 10.0; // STRAGGLAR_TIMEOUT_MS
@@ -96,6 +97,7 @@ inline Options read_options() {
   o.blocks = (int)env_int("STRAGGLAR_BLOCKS", 0);
   o.threads = (int)env_int("STRAGGLAR_THREADS", 0);
   o.stages = (int)env_int("STRAGGLAR_STAGES", 0);
+  o.store_window = (int)env_int("STRAGGLAR_STORE_WINDOW", 0);
   o.tile_bytes = (uint32_t)env_int("STRAGGLAR_TILE_BYTES", 0);
   o.timeout_s = env_int("STRAGGLAR_TIMEOUT_MS", 10000) / 1000.0;
   o.warmup = (int)env_int("STRAGGLAR_WARMUP", 10);

@@ -60,6 +60,7 @@ int sar_program_num_phases(const sar_program* p) { return (int)p->tables.size();
 const sar_table* sar_program_phase(const sar_program* p, int i) { return &p->tables[i]; }
 int sar_table_channel(const sar_table* t) { return t->c.channel; }
 int sar_table_blocks_hint(const sar_table* t) { return t->c.blocks_hint; }
+int sar_table_stages_hint(const sar_table* t) { return t->c.stages_hint; }
 int sar_table_gate_rounds(const sar_table* t) { return t->c.gate_rounds ? 1 : 0; }
 uint64_t sar_gate_min_bytes(void) { return sar::gate_min_bytes(); }
 int sar_table_lane1_eighths(const sar_table* t) { return t->c.lane1_eighths; }

@@ -56,12 +56,13 @@ static inline void store_elem(void* p, uint64_t i, SarDtype d, float v) {
 
 uint64_t gate_min_bytes() {
   const char* v = getenv("STRAGGLAR_GATE_MIN_BYTES");
-  return (v && *v) ? strtoull(v, nullptr, 10) : (48ull << 20);
+  return (v && *v) ? strtoull(v, nullptr, 10) : (128ull << 20);
 }
 
-uint32_t gate_slack() {
+uint32_t gate_slack(uint32_t tiles_per_chunk) {
   const char* v = getenv("STRAGGLAR_GATE_SLACK");
-  return (v && *v) ? (uint32_t)strtoul(v, nullptr, 10) : 0u;
+  if (v && *v) return (uint32_t)strtoul(v, nullptr, 10);
+  return (uint32_t)(((uint64_t)tiles_per_chunk * 3 + 5) / 10);
 }
 
 uint32_t pick_tile_elems(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t blocks, uint32_t min_bytes,
@@ -333,7 +334,7 @@ static uint32_t run_phases(const std::vector<const Compiled*>& phases, void* con
               l.geom = make_geom(count, esize, c.num_chunks, te);
               l.dtype = dtype; l.scale = scale; l.timeout_s = timeout_s; l.participants = c.participants;
               l.gate_rounds = c.gate_rounds;
-              l.gate_slack = gate_slack();
+              l.gate_slack = gate_slack(l.geom.tiles_per_chunk);
               l.gate_base = (uint64_t)(rep + 1) * SAR_VER_STRIDE;
               l.lane1_eighths = (uint32_t)c.lane1_eighths;
               l.epoch_base = (uint32_t)(rep + 1) * SAR_VER_STRIDE;

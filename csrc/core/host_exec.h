@@ -49,13 +49,18 @@ uint32_t host_execute(const Compiled& c, void* const* bufs, uint64_t count, SarD
 uint32_t host_execute_program(const Program& p, void* const* bufs, uint64_t count, SarDtype dtype, uint32_t tile_elems,
                               float scale, int blocks, const double* delay_ms, double timeout_s);
 
-// Round gating costs a hand-shake per round and pays once a round's chunk takes much longer than that on
-// the link: a gated table is launched with gating for buffers of at least this many bytes
-// (STRAGGLAR_GATE_MIN_BYTES, default 48 MiB: in the tile-level model of an 8-GPU box the gated rounds win
-// from 64 MiB up and lose at 32 MiB).  Every rank of a launch sees the same size, hence the same answer.
+// Round gating costs a hand-shake per round and pays once a round's chunk takes much longer than that on the
+// link: a gated table is launched with gating for buffers of at least this many bytes (STRAGGLAR_GATE_MIN_BYTES,
+// default 128 MiB; measured on 8 x B200: gated rounds win at 256 MiB and 1 GiB and lose at 64 MiB).  Every rank of
+// a launch sees the same size, hence the same answer.
 uint64_t gate_min_bytes();
-// STRAGGLAR_GATE_SLACK (default 0, see SAR_GATE_ALL_DONE in table.h); every rank must see the same value.
-uint32_t gate_slack();
+// Items of a round that may still be running when the next round opens: STRAGGLAR_GATE_SLACK if set (0 = full
+// barrier between rounds), else three tenths of a chunk's tiles, the middle of a flat optimum measured on 8 x B200
+// (1 GiB: 2.17-2.25 ms for slacks of 5-45 % of a chunk against 2.33-2.40 ms with the full barrier).
+uint32_t gate_slack(uint32_t tiles_per_chunk);
+// Upper bound of the tile size of a gated launch on the GPU: with the rounds kept apart there is little to gain
+// from fine-grained pipelining across rounds, and larger tiles mean fewer flag polls over the link.
+inline uint32_t gate_tile_bytes() { return 256u << 10; }
 
 uint32_t pick_tile_elems(uint64_t count, uint32_t esize, uint32_t num_chunks, uint32_t blocks, uint32_t min_bytes,
                          uint32_t max_bytes);

@@ -352,22 +352,23 @@ Plan plan_by_name(const std::string& alg, int n, bool prephase, const Schedule* 
   p.two_lanes = has_exchange && two_lanes_default_for(alg);
   p.split_copies = has_exchange;
   // Blocks per rank beyond which the collective gets slower (8 x B200, 1 GiB, after the arrival):
-  //   stragglar      48: -, 64: 2.42 ms, 96: 2.62, 128: 2.60
-  //   stragglar_a2a  32: 1.83 ms, 48: 1.83, 64: 2.00, 96: 2.45, 128: 2.64
+  //   stragglar, free-running rounds   32: 2.72 ms, 48: 2.72, 64: 2.46-2.56, 128: 2.60
+  //   stragglar, gated rounds          32: 2.32, 48: 2.21, 64: 2.17-2.25, 96: 2.17, 128: 2.22
+  //   stragglar_a2a                    24: 1.89, 32: 1.81, 48: 1.83, 64: 2.00, 128: 2.64; 48 blocks with three of
+  //                                    the six ring stages (fewer bytes in flight per block): 1.74
   // (more concurrent flows per link only add contention once the link is saturated);
   // ring / rhd / rsag keep improving up to 128.
   // With one or two ranks there is a single flow per link and more blocks keep helping.
   if (alg == "stragglar" && n >= 4) p.blocks_hint = 64;
-  if (alg == "stragglar_a2a" && n >= 4) p.blocks_hint = 32;
-  // Round gating pays for the synthesized schedule, whose rounds are matchings (a tile-level model of
-  // the executor puts it at 0.86-0.90 of the link rate against 0.73-0.78 with free-running rounds);
-  // the other algorithms lose a little to the extra hand-shake per round.  Opt-in until measured:
-  // STRAGGLAR_GATE=1 gates "stragglar", STRAGGLAR_GATE=all every algorithm, 0 none.
+  if (alg == "stragglar_a2a" && n >= 4) { p.blocks_hint = 48; p.stages_hint = 3; }
+  // Round gating (see SAR_GATE_ALL_DONE in table.h) pays for the synthesized schedule, whose rounds are matchings:
+  // one round at a time every port carries one flow in and one out.  8 x B200, 1 GiB after the arrival: 2.17-2.25 ms
+  // against 2.46-2.56 free-running; 256 MiB 0.71 against 0.77; 64 MiB 0.33 against 0.28, hence the size threshold
+  // (gate_min_bytes).  The other algorithms lose to the hand-shake per round (ring 3.19 against 2.87 ms).
+  // STRAGGLAR_GATE=0 switches it off, STRAGGLAR_GATE=all gates every algorithm.
+  p.gate_rounds = alg == "stragglar" && n >= 4;
   const char* gate = getenv("STRAGGLAR_GATE");
   if (gate && *gate) p.gate_rounds = !strcmp(gate, "all") || (atoi(gate) != 0 && alg == "stragglar" && n >= 4);
-  // one round at a time there is one flow per port whatever the block count, and the model keeps
-  // improving up to 128 blocks: the cap of the free-running lowering does not apply
-  if (p.gate_rounds && alg == "stragglar") p.blocks_hint = 0;
   // share of the blocks given to the forwarding lane (eighths); half unless STRAGGLAR_LANE1_EIGHTHS says otherwise
   // (forwarding moves n-2 chunks per chunk matched: the model of the executor prefers 5/8 at 32 blocks)
   const char* l1 = getenv("STRAGGLAR_LANE1_EIGHTHS");
@@ -599,6 +600,7 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
   }
   if (out.max_version >= (int)SAR_VER_STRIDE) throw CompileError("too many versions of one slot");
   out.blocks_hint = plan.blocks_hint;
+  out.stages_hint = plan.stages_hint;
   out.lane1_eighths = plan.lane1_eighths;
   for (int r = 0; r < (int)out.ranks.size(); ++r) {
     const std::string why = validate_rank_table(out.ranks[r], r, np, P);

@@ -66,6 +66,7 @@ struct Plan {
   Expect expect = Expect::AllReduce;
   bool push_copies = false;       // lower Copy steps as SAR_PUSH (executed by the source) instead of SAR_COPY
   int blocks_hint = 0;            // largest block count per rank worth using (0: no preference)
+  int stages_hint = 0;            // bulk-copy path: ring stages per block this plan runs best with (0: all)
   bool gate_rounds = false;       // run the rounds one after the other (see SAR_GATE_ALL_DONE in table.h)
   int lane1_eighths = 4;          // two lanes: share of the blocks that forwarding (lane 1) gets, in eighths
   bool two_lanes = false;         // forwarding ops go to lane 1 (their own blocks), the rest to lane 0
@@ -106,6 +107,7 @@ struct Compiled {
   int max_version = 0;
   int num_rounds = 0;
   int blocks_hint = 0;    // upper bound of the blocks per rank this table runs best with (0: none)
+  int stages_hint = 0;    // bulk-copy path: ring stages per block (0: all); fewer stages keep fewer bytes in flight
   bool gate_rounds = false;   // launch with round gating (every rank of a launch must agree)
   int lane1_eighths = 4;      // share of the blocks of lane 1, in eighths (see sar_lane_of_block)
   std::vector<RankTable> ranks;          // by physical rank

@@ -918,6 +918,7 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
     constexpr uint32_t CT = 32 * kConsumerWarps;
     uint32_t seq = 0;
     uint32_t landed = 0, pend_tail = 0;             // private copies of the storing thread (ctid 0)
+    const uint32_t win = P.store_window >= 16 ? 16u : (P.store_window >= 8 ? 8u : 3u);
     while (true) {
       const uint32_t s = seq % nst;
       bool ok = true;
@@ -1009,9 +1010,12 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         // the previous piece's stores have read their stage: hand it back
         bulk_wait_read<1>();
         if (seq >= 1) mbar_arrive(&S.empty[(seq - 1) % nst]);
-        // at most three store groups stay in flight; older ones have landed
-        bulk_wait_all<3>();
-        if (seq >= 3 && landed < seq - 2) { landed = seq - 2; st_release_cta(&S.landed, landed); }
+        // at most `win` store groups stay in flight; older ones have landed.  Stores to peer memory are
+        // posted: a deep window keeps a block's pushes from being paced by the link's round trip.
+        if (win >= 16) bulk_wait_all<16>();
+        else if (win >= 8) bulk_wait_all<8>();
+        else bulk_wait_all<3>();
+        if (seq >= win && landed < seq - (win - 1)) { landed = seq - (win - 1); st_release_cta(&S.landed, landed); }
       }
       ++seq;
     }

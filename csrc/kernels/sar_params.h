@@ -41,7 +41,7 @@ struct SarLaunchParams {
   uint32_t gate_slack;    // round gating: items of a round that may still be running when the next round opens
   uint64_t gate_base;     // round gating: value that stands for round 0 of this launch (grows by >= 32 per launch)
   uint32_t stages;        // bulk-copy path: ring stages in use (0 or > the ring size: all)
-  uint32_t pad1;
+  uint32_t store_window;  // bulk-copy path: store groups a block keeps in flight (3, 8 or 16; 0: 3)
   uint64_t delay_ns;      // spin this long before arriving (a late rank when ranks share one launch)
   SarMcGroup mc[2];       // multicast views (simt path): all ranks, and e.g. the non-stragglers
 };

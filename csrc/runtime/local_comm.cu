@@ -213,7 +213,9 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
     int pblocks = blocks;   // this phase's block count: the table may ask for fewer
     const int hint = sar_table_blocks_hint(t);
     if (o->blocks <= 0 && !c->emulate && hint > 0 && hint < pblocks) pblocks = hint;
-    const uint32_t tile_elems = sar_pick_tile_elems(count, esize, nch, (uint32_t)pblocks, 2048, tile_max);
+    const bool gated = sar_table_gate_rounds(t) && count * esize >= sar_gate_min_bytes();
+    const uint32_t ptile_max = (gated && !o->tile_bytes && !c->emulate) ? sar::gate_tile_bytes() : tile_max;
+    const uint32_t tile_elems = sar_pick_tile_elems(count, esize, nch, (uint32_t)pblocks, 2048, ptile_max);
     SarGeom g = sar::make_geom(count, esize, nch, tile_elems);
     if ((uint64_t)g.tiles_per_chunk * g.num_chunks > SAR_FLAG_CAPACITY) {
       if (err) snprintf(err, errlen, "buffer too large for the flag array");
@@ -238,9 +240,10 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
       P.epoch_base = (uint32_t)c->epoch[ch]; P.gate_base = c->epoch[ch]; P.scale = o->scale; P.dtype = dtype;
       P.timeout_ns = (uint64_t)(timeout_s * 1e9);
       P.status = rk.status; P.trace = rk.trace; P.trace_rounds = o->trace_rounds ? 1u : 0u;
-      P.gate_rounds = (sar_table_gate_rounds(t) && count * esize >= sar_gate_min_bytes()) ? 1u : 0u;
-      P.gate_slack = sar::gate_slack();
-      P.stages = o->stages > 0 ? (uint32_t)o->stages : 0u;
+      P.gate_rounds = gated ? 1u : 0u;
+      P.gate_slack = sar::gate_slack(g.tiles_per_chunk);
+      P.stages = o->stages > 0 ? (uint32_t)o->stages : (uint32_t)sar_table_stages_hint(t);
+      P.store_window = o->store_window > 0 ? (uint32_t)o->store_window : 0u;
       P.lane1_eighths = (uint32_t)sar_table_lane1_eighths(t);
       if (mc_alloc) {
         for (int grp = 0; grp < 2; ++grp) {

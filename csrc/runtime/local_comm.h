@@ -25,6 +25,7 @@ struct sar_run_opts {
   int timed;              // 1: bracket every rank's work with events after a device-side start barrier
   int trace_rounds;       // 1: keep per-round statistics of this run (see sar_local_round_trace)
   int stages;             // bulk-copy path: shared-memory ring stages per block (<= 0: all six)
+  int store_window;       // bulk-copy path: store groups a block keeps in flight: 3, 8 or 16 (<= 0: default)
 };
 
 // devices[r] is the CUDA device of rank r.  emulate != 0 places every rank on

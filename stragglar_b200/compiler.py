@@ -73,7 +73,7 @@ def lib():
             L.sar_host_execute_program.restype = C.c_uint32
             L.sar_host_execute_program.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_uint64, C.c_int, C.c_uint32,
                                                    C.c_float, C.c_int, C.POINTER(C.c_double), C.c_double]
-            for name in ("nranks", "num_chunks", "num_rounds", "max_version", "channel", "blocks_hint", "gate_rounds", "lane1_eighths"):
+            for name in ("nranks", "num_chunks", "num_rounds", "max_version", "channel", "blocks_hint", "stages_hint", "gate_rounds", "lane1_eighths"):
                 f = getattr(L, f"sar_table_{name}")
                 f.restype, f.argtypes = C.c_int, [C.c_void_p]
             for name in ("num_ops", "num_round_begin"):
@@ -121,6 +121,7 @@ class Table:
         self.max_version = L.sar_table_max_version(handle)
         self.channel = L.sar_table_channel(handle)
         self.blocks_hint = L.sar_table_blocks_hint(handle)
+        self.stages_hint = L.sar_table_stages_hint(handle)         # bulk-copy path: ring stages per block (0: all)
         self.gate_rounds = bool(L.sar_table_gate_rounds(handle))   # rounds run one after the other (STRAGGLAR_GATE)
         self.lane1_eighths = L.sar_table_lane1_eighths(handle)     # share of the blocks of lane 1 (4: half)
         self.participants = L.sar_table_participants(handle)

@@ -205,7 +205,8 @@ def test_every_lowering_gives_the_same_sum(monkeypatch, copy, lanes):
 
 def test_block_count_hints():
     assert sc.compile_table("stragglar", 8).blocks_hint == 64
-    assert sc.compile_table("stragglar_a2a", 8).blocks_hint == 32
+    a2a = sc.compile_table("stragglar_a2a", 8)
+    assert a2a.blocks_hint == 48 and a2a.stages_hint == 3
     assert sc.compile_table("ring", 8).blocks_hint == 0
     assert sc.compile_table("stragglar", 2).blocks_hint == 0 and sc.compile_table("stragglar", 1).blocks_hint == 0
     assert [t.blocks_hint for t in sc.compile_program("direct", 8).phases] == [0, 0]
@@ -225,7 +226,8 @@ def test_round_gating_attribute_and_host_execution(monkeypatch):
     from helpers import oracle_sum, seeded_inputs
 
     monkeypatch.delenv("STRAGGLAR_GATE", raising=False)
-    assert not sc.compile_program("stragglar", 8).main.gate_rounds
+    assert sc.compile_program("stragglar", 8).main.gate_rounds           # the default for the synthesized schedule
+    assert not sc.compile_program("stragglar_a2a", 8).main.gate_rounds
     monkeypatch.setenv("STRAGGLAR_GATE", "1")
     assert sc.compile_program("stragglar", 8).main.gate_rounds
     assert not sc.compile_program("stragglar", 2).main.gate_rounds       # one round: nothing to gate
