@@ -42,6 +42,21 @@ def default_bytes() -> int:
     return math.ceil(GIB / (1024 * 7)) * 1024 * 7
 
 
+def bench_bytes(requested: int, n: int, esize: int = 4) -> int:
+    """Bytes per GPU that both arms use: the request (default: 1 GiB rounded up to a multiple of 7 KiB), cut to a whole
+    number of elements per StragglAR chunk (n - 1 chunks), which the reference program needs
+    (stragglar/allreduce_8GPU.cu:877) and this library does not mind."""
+    nbytes = requested or default_bytes()
+    unit = esize * max(n - 1, 1)
+    return nbytes - nbytes % unit
+
+
+def bench_config(alg: str, n: int, nbytes: int, delay_ms: float, straggler: int) -> dict:
+    """The `config` entry of the JSON line; the same for both arms (what differs between them is said under `notes`)."""
+    return {"model": f"allreduce {alg}", "bytes_per_gpu": nbytes, "delay_ms": delay_ms, "straggler_rank": straggler,
+            "global_batch": None, "seq_len": None, "parallelism": f"dp{n}", "l2": "buffer per GPU larger than L2"}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU while a region runs."""
 
@@ -89,7 +104,7 @@ class ClockSampler:
 
 def reference_backend_e2e(args) -> dict:
     """The end-to-end step through the reference's own c10d backend (baseline/ref_backend_e2e.py), run as eight
-    processes of its own.  Opt-in (STRAGGLAR_REF_E2E=1): the backend is written for exactly 8 ranks."""
+    processes of its own (the backend is written for exactly 8 ranks).  STRAGGLAR_REF_E2E=0 skips it."""
     script = os.path.join(ROOT, "baseline", "ref_backend_e2e.py")
     port = 20000 + (os.getpid() % 20000)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "8", "--master-addr", "127.0.0.1",
@@ -99,9 +114,9 @@ def reference_backend_e2e(args) -> dict:
            if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_PORT", "MASTER_ADDR", "GROUP_RANK", "ROLE_RANK",
                         "LOCAL_WORLD_SIZE", "ROLE_WORLD_SIZE", "TORCHELASTIC_RUN_ID")}
     try:
-        p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     except subprocess.TimeoutExpired:
-        return {"unavailable": "the reference backend did not finish its end-to-end steps within 600 s"}
+        return {"unavailable": "the reference backend did not finish its end-to-end steps within 300 s"}
     for line in reversed(p.stdout.splitlines()):
         line = line.strip()
         if line.startswith("{") and "ms_per_step" in line:
@@ -136,12 +151,11 @@ def run_reference(args) -> int:
             time.sleep(0.5)
         return 0
     try:
-        nbytes = args.bytes or default_bytes()
-        # chunk = bytes / 4 / (n-1) elements must be whole
-        nbytes -= nbytes % (4 * (n - 1))
+        nbytes = bench_bytes(args.bytes, n)
         with ClockSampler(0) as cs:
             t0 = time.time()
-            p = subprocess.run([exe, str(nbytes), args.alg, str(args.steps), str(args.delay_ms)], capture_output=True,
+            # the program discards its iteration 0 (stragglar/allreduce_8GPU.cu:1053): one more, so that `steps` are timed
+            p = subprocess.run([exe, str(nbytes), args.alg, str(args.steps + 1), str(args.delay_ms)], capture_output=True,
                                text=True, timeout=1800)
             wall = time.time() - t0
         rows = [l.split(",") for l in p.stdout.splitlines() if l.startswith(args.alg + ",")]
@@ -151,19 +165,21 @@ def run_reference(args) -> int:
             return 0
         e2e = {"unavailable": "the reference program fills its buffers on the device and reads nothing back: it has "
                               "no host path to time (stragglar/allreduce_8GPU.cu:1010-1020)"}
-        if os.environ.get("STRAGGLAR_REF_E2E", "0") == "1" and n == 8 and args.alg == "stragglar":
+        if n == 8 and args.alg == "stragglar" and not args.no_e2e and os.environ.get("STRAGGLAR_REF_E2E", "1") != "0":
             e2e = reference_backend_e2e(args)
         ms = statistics.mean(float(r[4]) for r in rows)
         delay = max(args.delay_ms, 0.0)
         value = n * nbytes / 1e9 / ((ms - delay) / 1e3)
         out.update({"metric": "allreduce_aggregate_GBps", "value": value, "unit": "GB/s", "n_gpus": n, "steps": len(rows),
-                    "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                    "dtype": "fp32", "data": "constant fill (rank r holds r+1), as the reference program does",
+                    "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                    "dtype": "fp32", "data": "synthetic: constant fill (rank r holds r+1), as the reference program does",
                     "clocks": cs.summary(), "wall_s": wall,
                     "e2e": e2e,
-                    "config": {"model": f"allreduce {args.alg}", "bytes_per_gpu": nbytes, "delay_ms": args.delay_ms,
-                               "timing": "device 0 events only (the reference's own clock), nominal delay subtracted",
-                               "parallelism": f"1 process x {n} GPUs, NCCL send/recv"}})
+                    "config": bench_config(args.alg, n, nbytes, args.delay_ms, n - 1),
+                    "notes": {"timing": "device 0 events only (the reference's own clock), nominal delay subtracted",
+                              "warmup": "the program's own: 10 send/recv exchanges and a discarded first iteration, "
+                                        "whatever --warmup says (stragglar/allreduce_8GPU.cu:992-1006,1053)",
+                              "processes": f"1 process x {n} GPUs, NCCL send/recv"}})
         print(json.dumps(out), flush=True)
     finally:
         open(done, "w").close()
@@ -173,44 +189,6 @@ def run_reference(args) -> int:
         except OSError:
             pass
     return 0
-
-
-def experimental_lowerings(world: int, nbytes: int, delay_ms: float, straggler: int = -1) -> dict:
-    """Lowerings that are compiled in but not the default yet, timed by the library's own benchmark program
-    (bin/allreduce: one process, one rank per GPU, device time, max over ranks, every iteration verified) before
-    this process group touches a GPU: round gating for `stragglar`, a 5/8 lane split for `stragglar_a2a`.
-    Informational; a run that fails or takes too long is reported as such and changes nothing else."""
-    exe = os.path.join(ROOT, "bin", "allreduce")
-    if world < 4 or not os.path.exists(exe) or os.environ.get("STRAGGLAR_BENCH_EXPERIMENTS", "1") != "1":
-        return {}
-    out = {}
-    runs = (("stragglar_gated", "stragglar", {"STRAGGLAR_GATE": "1"}),
-            ("stragglar_default_lowering", "stragglar", {}),
-            ("stragglar_a2a_lane1_5of8", "stragglar_a2a", {"STRAGGLAR_LANE1_EIGHTHS": "5"}))
-    for name, alg, env in runs:
-        e = dict(os.environ, STRAGGLAR_NGPUS=str(world), STRAGGLAR_WARMUP="3", **env)
-        if straggler >= 0:
-            e["STRAGGLAR_STRAGGLER"] = str(straggler)
-        for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
-            e.pop(k, None)
-        try:
-            p = subprocess.run([exe, str(nbytes), alg, "8", "-1" if delay_ms <= 0 else f"-1,{delay_ms:g}"],
-                               capture_output=True, text=True, timeout=60, env=e)
-        except subprocess.TimeoutExpired:
-            out[name] = {"error": "timed out after 60 s"}
-            continue
-        rows = [l.split(",") for l in p.stdout.splitlines() if l.startswith(alg + ",")]
-        if p.returncode != 0 or not rows:
-            out[name] = {"error": f"exit {p.returncode}: {(p.stderr or p.stdout).strip()[-160:]!r}"}
-            continue
-        res = {"program": "bin/allreduce", "env": env}
-        for delay in sorted({r[3] for r in rows}):
-            net = [float(r[4]) - float(r[13]) for r in rows if r[3] == delay and len(r) > 13]
-            if net:
-                ms = statistics.median(net)
-                res[f"delay_{delay}"] = {"time_us_net": ms * 1e3, "algbw_GBps": nbytes / 1e9 / (ms / 1e3)}
-        out[name] = res
-    return out
 
 
 def main() -> int:
@@ -254,15 +232,10 @@ def main() -> int:
     dev = torch.device("cuda", local)
     dtype = getattr(torch, args.dtype)
     esize = torch.empty(0, dtype=dtype).element_size()
-    nbytes = args.bytes or default_bytes()
+    nbytes = bench_bytes(args.bytes, world, esize)
     count = nbytes // esize
-    nbytes = count * esize
     straggler = args.straggler if args.straggler >= 0 else world - 1
     delay_ms = args.delay_ms if world > 1 else 0.0
-
-    # rank 0 first times the not-yet-default lowerings with the library's benchmark program (the other ranks wait
-    # in the rendezvous below and have not touched their GPUs yet)
-    experiments = experimental_lowerings(world, nbytes, delay_ms, args.straggler) if rank == 0 and args.alg == "stragglar" else {}
 
     os.environ.setdefault("STRAGGLAR_STAGING_MB", "64")
     os.environ.setdefault("STRAGGLAR_ARENA_MB", str(int(nbytes / (1 << 20)) + 64 + 64))
@@ -394,17 +367,16 @@ def main() -> int:
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": {"float32": "fp32", "bfloat16": "bf16", "float16": "fp16"}[args.dtype],
             "data": "synthetic: uniform[-1,1) seeded per rank, averaged in place every step (first step verified)",
-            "config": {"model": f"allreduce {args.alg}", "bytes_per_gpu": nbytes, "delay_ms": delay_ms,
-                       "straggler_rank": straggler, "global_batch": None, "seq_len": None,
-                       "parallelism": f"{world} ranks, one per GPU, own peer-memory kernels over NVLink",
-                       "l2": "buffer per GPU larger than L2", "impl": "ours"},
+            "config": bench_config(args.alg, world, nbytes, args.delay_ms if world > 1 else 0.0, straggler),
+            "notes": {"processes": f"{world} ranks, one per GPU, own peer-memory kernels over NVLink",
+                      "timing": "CUDA events on every rank, max over ranks, measured delay subtracted"},
             "time_us_net": net_ms * 1e3, "real_delay_ms": real_delay,
             "algbw_GBps": nbytes / 1e9 / (net_ms / 1e3),
             "busbw_GBps": nbytes / 1e9 / (net_ms / 1e3) * 2 * (world - 1) / world,
             "roofline_frac_of_measured": roof_ms / net_ms if net_ms > 0 else None,
             "roofline": ("busiest rank's bytes per direction / 770 GB/s measured peer copy" if world > 1
                          else "read+write of the buffer / 6532.5 GB/s measured copy"),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours", "variants": variants, "experimental_lowerings": experiments,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours", "variants": variants,
         }
         print(json.dumps(out), flush=True)
     dist.destroy_process_group()
