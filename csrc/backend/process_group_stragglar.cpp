@@ -12,6 +12,7 @@
 #include <cstring>
 #include <thread>
 
+#include "../core/c_api.h"
 #include "../core/host_exec.h"
 #include "../kernels/sar_cuda.h"
 #include "../kernels/sar_params.h"
@@ -58,15 +59,42 @@ WorkStragglar::WorkStragglar(int rank, c10d::OpType op, std::vector<at::Tensor> 
     : c10d::Work(rank, op), outputs_(std::move(outputs)), cuda_(cuda) {}
 
 bool WorkStragglar::isCompleted() { return !cuda_ || !end_ || end_->query(); }
-bool WorkStragglar::isSuccess() const { return true; }
+bool WorkStragglar::isSuccess() const {
+  if (error_) return false;
+  if (!cuda_ || !end_ || !fail_ || !end_->query()) return !cuda_ || !end_;   // CUDA work in flight: not known yet
+  return *(volatile uint32_t*)fail_->word.get() == 0;
+}
+void WorkStragglar::check_failure() {
+  if (!fail_) return;
+  const uint32_t st = *(volatile uint32_t*)fail_->word.get();
+  if (!st) return;
+  fail_->reported.store(true);
+  TORCH_CHECK(false, "stragglar backend: a collective failed on rank ", rank_, ": ", sar_status_string(st),
+              " (a device-side wait ran out; the result is incomplete)");
+}
+// Makes the caller's stream wait for the collective (the c10d contract for CUDA work).  With a timeout the host
+// waits too, at most that long.  Whenever the collective is known to have ended, a failure that the device
+// recorded (a wait that ran out because a peer was late or never came) is raised here.
 bool WorkStragglar::wait(std::chrono::milliseconds timeout) {
+  if (error_) std::rethrow_exception(error_);
   if (cuda_ && end_) {
     end_->block(c10::cuda::getCurrentCUDAStream(end_->device_index()));
-    if (timeout != kNoTimeout) end_->synchronize();
+    if (timeout != kNoTimeout) {
+      const auto deadline = std::chrono::steady_clock::now() + timeout;
+      while (!end_->query()) {
+        TORCH_CHECK(std::chrono::steady_clock::now() < deadline, "stragglar backend: the collective did not finish within ",
+                    timeout.count(), " ms");
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+      }
+    }
+    if (end_->query()) check_failure();
   }
   return true;
 }
-void WorkStragglar::synchronize() { wait(); }
+void WorkStragglar::synchronize() {
+  wait();
+  if (cuda_ && end_) { end_->synchronize(); check_failure(); }
+}
 c10::intrusive_ptr<c10::ivalue::Future> WorkStragglar::getFuture() { return future_; }
 
 // --------------------------------------------------------------- process group
@@ -166,12 +194,18 @@ ProcessGroupStragglar::Side& ProcessGroupStragglar::side(bool cuda, int device) 
   if (!staging) staging = cuda ? std::min<size_t>(arena / 4, (size_t)256 << 20) : arena / 2;
   s.device = device;
   s.t = std::make_unique<Transport>(cuda, device, getRank(), getSize(), arena, staging, store_, prefix_ + (cuda ? "/cuda" : "/cpu"));
-  if (cuda) s.stream = c10::cuda::getStreamFromPool(/*isHighPriority=*/true, (c10::DeviceIndex)device);
+  if (cuda) {
+    s.stream = c10::cuda::getStreamFromPool(/*isHighPriority=*/true, (c10::DeviceIndex)device);
+    s.fail = std::make_shared<FailureState>();
+    s.fail->word = s.t->status_owner();
+  }
   return s;
 }
 
 c10::intrusive_ptr<WorkStragglar> ProcessGroupStragglar::begin(Side& s, c10d::OpType op, std::vector<at::Tensor> outputs) {
+  recover_if_failed(s);
   auto w = c10::make_intrusive<WorkStragglar>(getRank(), op, std::move(outputs), s.t->cuda());
+  w->fail_ = s.fail;
   if (s.t->cuda()) {
     // the communication stream picks up after whatever the caller has queued
     at::cuda::CUDAEvent ready;
@@ -196,6 +230,35 @@ void ProcessGroupStragglar::finish(Side& s, const c10::intrusive_ptr<WorkStraggl
     w->future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
     w->future_->markCompleted(at::IValue(w->outputs_));
   }
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::failed(Side& s, const c10::intrusive_ptr<WorkStragglar>& w) {
+  if (s.t->cuda()) throw;   // CUDA launches fail for host-side reasons only (bad arguments): raise at once
+  w->error_ = std::current_exception();
+  w->future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+  w->future_->setError(w->error_);
+  return w;
+}
+
+void ProcessGroupStragglar::clear_failure(Side& s) {
+  SAR_CUDA_CHECK(cudaSetDevice(s.device));
+  SAR_CUDA_CHECK(cudaStreamSynchronize(s.stream->stream()));   // every block of the failed launch has returned
+  *(volatile uint32_t*)s.t->status() = 0;
+  for (int ch = 0; ch < SAR_NUM_CHANNELS; ++ch) {
+    SAR_CUDA_CHECK(cudaMemset(&s.t->ctrl(getRank(), ch)->abort_flag, 0, 4));
+    SAR_CUDA_CHECK(cudaMemset(&s.t->ctrl(getRank(), ch)->blocks_done, 0, 4));
+    SAR_CUDA_CHECK(cudaMemset(&s.t->ctrl(getRank(), ch)->items_done, 0, 8));
+  }
+}
+
+void ProcessGroupStragglar::recover_if_failed(Side& s) {
+  if (!s.t || !s.t->cuda() || !s.fail) return;
+  const uint32_t st = *(volatile uint32_t*)s.t->status();
+  if (!st) return;
+  clear_failure(s);
+  if (s.fail->reported.exchange(false)) return;   // a Work has raised for it already
+  TORCH_CHECK(false, "stragglar backend: an earlier collective failed on rank ", getRank(), ": ", sar_status_string(st),
+              " (a device-side wait ran out; its result is incomplete)");
 }
 
 void ProcessGroupStragglar::copy_local(Side& s, void* dst, const void* src, size_t bytes) {
@@ -292,7 +355,7 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.geom = g; P.rank = me; P.nranks = n; P.participants = c.participants;
       P.epoch_base = epoch; P.scale = scale; P.dtype = dt;
       P.timeout_ns = (uint64_t)(opts_.timeout_s * 1e9);
-      P.status = t.status(); P.trace = reinterpret_cast<uint64_t*>(t.status() + 4); P.delay_ns = 0;
+      P.status = t.status(); P.trace = t.trace_words(); P.delay_ns = 0;
       P.gate_rounds = gated ? 1u : 0u;
       P.gate_base = epoch64; P.gate_slack = sar::gate_slack(g.tiles_per_chunk);
       P.stages = (uint32_t)c.stages_hint;
@@ -328,15 +391,8 @@ int64_t ProcessGroupStragglar::check_status(bool cuda) {
   if (!s.t || !cuda) return 0;
   SAR_CUDA_CHECK(cudaSetDevice(s.device));
   SAR_CUDA_CHECK(cudaStreamSynchronize(s.stream->stream()));
-  uint32_t st = 0;
-  SAR_CUDA_CHECK(cudaMemcpy(&st, s.t->status(), 4, cudaMemcpyDeviceToHost));
-  if (st) {
-    SAR_CUDA_CHECK(cudaMemset(s.t->status(), 0, 4));
-    for (int ch = 0; ch < SAR_NUM_CHANNELS; ++ch) {
-      SAR_CUDA_CHECK(cudaMemset(&s.t->ctrl(getRank(), ch)->abort_flag, 0, 4));
-      SAR_CUDA_CHECK(cudaMemset(&s.t->ctrl(getRank(), ch)->blocks_done, 0, 4));
-    }
-  }
+  const uint32_t st = *(volatile uint32_t*)s.t->status();
+  if (st) { clear_failure(s); s.fail->reported.store(false); }
   return st;
 }
 
@@ -352,7 +408,7 @@ std::pair<int64_t, int64_t> ProcessGroupStragglar::last_trace() {
   SAR_CUDA_CHECK(cudaSetDevice(s.device));
   SAR_CUDA_CHECK(cudaStreamSynchronize(s.stream->stream()));
   uint64_t v[2] = {0, 0};
-  SAR_CUDA_CHECK(cudaMemcpy(v, s.t->status() + 4, 16, cudaMemcpyDeviceToHost));
+  SAR_CUDA_CHECK(cudaMemcpy(v, s.t->trace_words(), 16, cudaMemcpyDeviceToHost));
   return {(int64_t)v[0], (int64_t)v[1]};
 }
 
@@ -415,10 +471,14 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allreduce(std::vector<at::
   std::lock_guard<std::mutex> lk(mu_);
   Side& s = side(tensors[0]);
   auto w = begin(s, c10d::OpType::ALLREDUCE, tensors);
-  if (table_dtype(tensors[0].scalar_type()) && table_op(opts.reduceOp))
-    allreduce_impl(s, tensors[0], scale_for(opts.reduceOp, getSize()), std::nullopt);
-  else
-    allreduce_generic(s, tensors[0], opts.reduceOp);
+  try {
+    if (table_dtype(tensors[0].scalar_type()) && table_op(opts.reduceOp))
+      allreduce_impl(s, tensors[0], scale_for(opts.reduceOp, getSize()), std::nullopt);
+    else
+      allreduce_generic(s, tensors[0], opts.reduceOp);
+  } catch (const std::exception&) {
+    return failed(s, w);
+  }
   finish(s, w);
   return w;
 }
@@ -429,7 +489,11 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::allreduce_ex(at::Tensor& t
   std::lock_guard<std::mutex> lk(mu_);
   Side& s = side(tensor);
   auto w = begin(s, c10d::OpType::ALLREDUCE, {tensor});
-  allreduce_impl(s, tensor, average ? 1.0f / (float)getSize() : 1.0f, comm_dtype);
+  try {
+    allreduce_impl(s, tensor, average ? 1.0f / (float)getSize() : 1.0f, comm_dtype);
+  } catch (const std::exception&) {
+    return failed(s, w);
+  }
   finish(s, w);
   return w;
 }

@@ -27,6 +27,8 @@
 #include <ATen/cuda/CUDAEvent.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <atomic>
+#include <exception>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -50,6 +52,14 @@ struct BackendOptions {
   std::string schedule_text;       // overrides the built-in StragglAR schedule
 };
 
+// The failure word of one device side of a process group, shared with the Work objects it hands out.
+// `reported`: a Work has already raised for the failure that the word shows, so the process group clears
+// it silently before its next collective instead of raising a second time.
+struct FailureState {
+  std::shared_ptr<uint32_t> word;   // pinned host memory written by the device (see Transport::status)
+  std::atomic<bool> reported{false};
+};
+
 class WorkStragglar : public c10d::Work {
  public:
   WorkStragglar(int rank, c10d::OpType op, std::vector<at::Tensor> outputs, bool cuda);
@@ -64,8 +74,11 @@ class WorkStragglar : public c10d::Work {
   friend class ProcessGroupStragglar;
   std::vector<at::Tensor> outputs_;
   bool cuda_;
+  void check_failure();             // raises when the device has recorded a failed wait
   std::shared_ptr<at::cuda::CUDAEvent> end_;
   c10::intrusive_ptr<c10::ivalue::Future> future_;
+  std::shared_ptr<FailureState> fail_;
+  std::exception_ptr error_;        // a failure that happened while the work was issued (CPU tensors run at once)
 };
 
 class ProcessGroupStragglar : public c10d::Backend {
@@ -141,6 +154,7 @@ class ProcessGroupStragglar : public c10d::Backend {
   struct Side {   // per device type
     std::unique_ptr<Transport> t;
     std::optional<c10::cuda::CUDAStream> stream;
+    std::shared_ptr<FailureState> fail;
     int device = -1;
     std::vector<std::shared_ptr<void>> dev_tables;   // keeps uploaded tables alive
     std::map<std::pair<const void*, int>, std::pair<void*, void*>> uploaded;  // (table, rank) -> ops, round_begin
@@ -152,6 +166,11 @@ class ProcessGroupStragglar : public c10d::Backend {
   void device_barrier(Side& s);
   c10::intrusive_ptr<WorkStragglar> begin(Side& s, c10d::OpType op, std::vector<at::Tensor> outputs);
   void finish(Side& s, const c10::intrusive_ptr<WorkStragglar>& w);
+  // CPU tensors are reduced inside the call: a failure there (a rank that never joined) becomes the Work's
+  // error, raised by wait(), as it is for CUDA tensors
+  c10::intrusive_ptr<c10d::Work> failed(Side& s, const c10::intrusive_ptr<WorkStragglar>& w);
+  void recover_if_failed(Side& s);  // raises for a failure nobody has been told about, then clears it
+  void clear_failure(Side& s);
   void copy_local(Side& s, void* dst, const void* src, size_t bytes);
   void pull(Side& s, const std::vector<std::tuple<int, size_t, void*, size_t>>& segs);  // (peer, offset in data region, dst, bytes)
   void allreduce_impl(Side& s, at::Tensor& t, float scale, std::optional<at::ScalarType> comm_dtype);

@@ -53,6 +53,12 @@ void Transport::open_arenas(const c10::intrusive_ptr<c10d::Store>& store, const 
     SAR_CUDA_CHECK(cudaMemset((char*)p + ArenaLayout::kDataOff + data_bytes_, ArenaLayout::kGuardByte, ArenaLayout::kGuardBytes));
     SAR_CUDA_CHECK(cudaDeviceSynchronize());
     base_[rank] = (char*)p;
+    {
+      void* hs = nullptr;
+      SAR_CUDA_CHECK(cudaHostAlloc(&hs, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+      memset(hs, 0, 64);
+      host_status_ = std::shared_ptr<uint32_t>((uint32_t*)hs, [](uint32_t* q) { cudaFreeHost(q); });
+    }
     if (n > 1) {
       cudaIpcMemHandle_t h;
       SAR_CUDA_CHECK(cudaIpcGetMemHandle(&h, p));

@@ -64,7 +64,13 @@ class Transport {
     return reinterpret_cast<uint32_t*>(base_[r] + ArenaLayout::kFlagsOff) + (size_t)channel * SAR_FLAG_CAPACITY;
   }
   SarCtrl* ctrl(int r, int channel) const { return reinterpret_cast<SarCtrl*>(base_[r] + ArenaLayout::kCtrlOff) + channel; }
-  uint32_t* status() const { return reinterpret_cast<uint32_t*>(base_[rank_] + ArenaLayout::kStatusOff); }
+  // This rank's failure word (a SarStatus; 0 = ok).  On CUDA it lives in pinned host memory that the device
+  // writes through a mapped pointer, so the host can look at it at any time without a CUDA call; kernels write
+  // it only when a wait runs out.
+  uint32_t* status() const { return host_status_ ? host_status_.get() : reinterpret_cast<uint32_t*>(base_[rank_] + ArenaLayout::kStatusOff); }
+  std::shared_ptr<uint32_t> status_owner() const { return host_status_; }
+  // arrival / end stamps of the last collective kernel (device memory on CUDA)
+  uint64_t* trace_words() const { return reinterpret_cast<uint64_t*>(base_[rank_] + ArenaLayout::kStatusOff + 16); }
   size_t data_bytes() const { return data_bytes_; }
   size_t staging_bytes() const { return staging_bytes_; }
   size_t staging_off() const { return data_bytes_ - staging_bytes_; }   // staging sits at the end of the data region
@@ -97,6 +103,7 @@ class Transport {
   uint32_t barrier_epoch_ = 0;
   std::string shm_name_;
   std::shared_ptr<Heap> heap_;
+  std::shared_ptr<uint32_t> host_status_;   // CUDA: pinned, mapped
 };
 
 }  // namespace sarpg

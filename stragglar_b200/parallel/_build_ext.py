@@ -26,6 +26,7 @@ HOST_SOURCES = [
     os.path.join(CSRC, "backend", "transport.cpp"),
     os.path.join(CSRC, "core", "plan.cpp"),
     os.path.join(CSRC, "core", "host_exec.cpp"),
+    os.path.join(CSRC, "core", "c_api.cpp"),
 ]
 CUDA_SOURCES = [os.path.join(CSRC, "kernels", "exec_table.cu")]
 
@@ -36,6 +37,7 @@ def _deps() -> List[str]:
         if os.path.basename(base) in ("bench", "runtime"):
             continue
         out += [os.path.join(base, f) for f in files]
+    out.append(os.path.abspath(__file__))   # the source list lives here
     return out
 
 

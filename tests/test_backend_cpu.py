@@ -188,8 +188,11 @@ def _late_rank_times_out(rank, world):
     dist.barrier()   # the arenas exist from here on
     if rank == 0:
         t0 = time.time()
+        # the failure belongs to the Work: issuing the collective returns, wait() raises, is_success() is false
+        work = dist.all_reduce(torch.ones(64), async_op=True)
         with pytest.raises(RuntimeError, match="collective failed|timed out"):
-            dist.all_reduce(torch.ones(64))
+            work.wait()
+        assert not work.is_success()
         assert time.time() - t0 < 5.0
     else:
         time.sleep(0.35)  # joins the final barrier while rank 0 is still giving up on the all-reduce

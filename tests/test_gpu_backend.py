@@ -172,3 +172,41 @@ def _monitor(rank, world):
 @pytest.mark.multigpu
 def test_straggler_monitor_relabels_the_schedule():
     run_ranks(min(torch.cuda.device_count(), 4) // 2 * 2, _monitor)
+
+
+def _late_rank_cuda(rank, world):
+    """Rank 1 comes a second late to one collective while every device-side wait is limited to 200 ms: on both ranks
+    the Work raises, nothing hangs, and the next collective is correct.  Nobody leaves; the failure is made on the
+    host (a sleep), never on the device."""
+    import datetime
+    import time
+    import stragglar_b200.parallel as sp
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    x = torch.full((1 << 16,), float(rank + 1), device=dev)
+    dist.all_reduce(x)                       # arenas exist, the ranks are aligned
+    torch.cuda.synchronize()
+    assert float(x[0]) == 3.0
+    if rank == 1:
+        time.sleep(1.0)
+    y = torch.full((1 << 16,), float(rank + 1), device=dev)
+    work = dist.all_reduce(y, async_op=True)
+    with pytest.raises(RuntimeError, match="collective failed"):
+        work.wait(datetime.timedelta(seconds=10))
+    assert work.is_completed() and not work.is_success()
+    time.sleep(1.5 if rank == 0 else 0.2)    # both ranks have given up before anybody goes on
+    z = torch.full((1 << 16,), float(rank + 1), device=dev)
+    work = dist.all_reduce(z, async_op=True)
+    work.wait(datetime.timedelta(seconds=10))
+    assert work.is_success() and float(z[0]) == 3.0 and float(z[-1]) == 3.0
+    assert sp.check_status(dev) == 0
+
+
+@pytest.mark.multigpu
+def test_late_rank_raises_through_the_work_object():
+    os.environ["STRAGGLAR_TIMEOUT_MS"] = "200"
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        run_ranks(2, _late_rank_cuda)
+    finally:
+        del os.environ["STRAGGLAR_TIMEOUT_MS"]
