@@ -175,7 +175,7 @@ def test_straggler_monitor_relabels_the_schedule():
 
 
 def _late_rank_cuda(rank, world):
-    """Rank 1 comes a second late to one collective while every device-side wait is limited to 200 ms: on both ranks
+    """Rank 1 comes 1.5 s late to one collective while every device-side wait is limited to 400 ms: on both ranks
     the Work raises, nothing hangs, and the next collective is correct.  Nobody leaves; the failure is made on the
     host (a sleep), never on the device."""
     import datetime
@@ -187,14 +187,15 @@ def _late_rank_cuda(rank, world):
     dist.all_reduce(x)                       # arenas exist, the ranks are aligned
     torch.cuda.synchronize()
     assert float(x[0]) == 3.0
+    t0 = time.time()                         # the ranks are within milliseconds of one another here
     if rank == 1:
-        time.sleep(1.0)
+        time.sleep(1.5)
     y = torch.full((1 << 16,), float(rank + 1), device=dev)
     work = dist.all_reduce(y, async_op=True)
     with pytest.raises(RuntimeError, match="collective failed"):
         work.wait(datetime.timedelta(seconds=10))
     assert work.is_completed() and not work.is_success()
-    time.sleep(1.5 if rank == 0 else 0.2)    # both ranks have given up before anybody goes on
+    time.sleep(max(0.0, t0 + 2.6 - time.time()))   # both ranks have given up (by 1.9 s) before anybody goes on
     z = torch.full((1 << 16,), float(rank + 1), device=dev)
     work = dist.all_reduce(z, async_op=True)
     work.wait(datetime.timedelta(seconds=10))
@@ -204,7 +205,7 @@ def _late_rank_cuda(rank, world):
 
 @pytest.mark.multigpu
 def test_late_rank_raises_through_the_work_object():
-    os.environ["STRAGGLAR_TIMEOUT_MS"] = "200"
+    os.environ["STRAGGLAR_TIMEOUT_MS"] = "400"
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     try:
         run_ranks(2, _late_rank_cuda)
