@@ -61,6 +61,12 @@ const sar_table* sar_program_phase(const sar_program* p, int i) { return &p->tab
 int sar_table_channel(const sar_table* t) { return t->c.channel; }
 int sar_table_blocks_hint(const sar_table* t) { return t->c.blocks_hint; }
 int sar_table_stages_hint(const sar_table* t) { return t->c.stages_hint; }
+void sar_table_final_ver(const sar_table* t, int rank, uint8_t* out) {
+  for (int c = 0; c < SAR_MAX_CHUNKS; ++c) out[c] = 0;
+  if (rank < 0 || rank >= (int)t->c.ranks.size()) return;
+  const auto& fv = t->c.ranks[rank].final_ver;
+  for (size_t c = 0; c < fv.size() && c < SAR_MAX_CHUNKS; ++c) out[c] = fv[c];
+}
 int sar_table_gate_rounds(const sar_table* t) { return t->c.gate_rounds ? 1 : 0; }
 uint64_t sar_gate_min_bytes(void) { return sar::gate_min_bytes(); }
 int sar_table_lane1_eighths(const sar_table* t) { return t->c.lane1_eighths; }

@@ -34,6 +34,8 @@ uint64_t sar_gate_min_bytes(void);
 // 0 when rank's table is well-formed for a communicator of nranks (see validate_rank_table); else 1 and the reason
 int sar_table_validate(const sar_table* t, int rank, int nranks, char* err, int errlen);
 int sar_table_lane1_eighths(const sar_table* t);   // share of the blocks of lane 1, in eighths (4: half)
+// out[c] (SAR_MAX_CHUNKS entries): the version rank `rank`'s slot of chunk c has when the collective is done
+void sar_table_final_ver(const sar_table* t, int rank, uint8_t* out);
 int sar_table_stages_hint(const sar_table* t);   // 0, or the ring stages per block the bulk-copy path should use
 int sar_table_blocks_hint(const sar_table* t);   // 0, or the largest block count per rank worth using
 uint32_t sar_table_participants(const sar_table* t);

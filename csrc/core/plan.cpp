@@ -657,6 +657,8 @@ Compiled compile(const Plan& plan, const std::vector<int>& l2p_in, int n_physica
     for (size_t q = 0; q < t.ops.size(); ++q)
       if (t.ops[q].round != last) { t.round_begin.push_back((uint16_t)q); last = t.ops[q].round; }
     t.round_begin.push_back((uint16_t)t.ops.size());
+    t.final_ver.assign(P, 0);
+    for (int c = 0; c < P; ++c) t.final_ver[c] = (uint8_t)slot[lr][c].ver;
   }
   return out;
 }

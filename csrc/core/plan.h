@@ -96,6 +96,7 @@ bool default_two_lanes();
 struct RankTable {
   std::vector<SarOp> ops;
   std::vector<uint16_t> round_begin;  // ops [round_begin[i], round_begin[i+1]) form the i-th non-empty round
+  std::vector<uint8_t> final_ver;     // per chunk: version of this rank's slot when the collective is done
 };
 
 struct Compiled {

@@ -50,7 +50,12 @@
 #define SAR_FLAG_CAPACITY (1u << 18)     // flags per rank and channel
 #define SAR_VEC_BYTES 16
 
-enum SarOpKind : uint8_t { SAR_COPY = 0, SAR_REDUCE = 1, SAR_REDUCE_PUSH = 2, SAR_PUSH = 3 };
+enum SarOpKind : uint8_t { SAR_COPY = 0, SAR_REDUCE = 1, SAR_REDUCE_PUSH = 2, SAR_PUSH = 3,
+                           // Never in a table: the executors add them around a table when the caller's tensor is not the
+                           // buffer that peers can reach.  STAGE_IN copies a tile of the caller's input into the own
+                           // slot (casting to the wire type) and announces it as version 0; STAGE_OUT copies a tile
+                           // whose slot has reached its final version into the caller's output (casting back).
+                           SAR_STAGE_IN = 4, SAR_STAGE_OUT = 5 };
 enum SarOpFlag : uint8_t {
   SAR_F_SCALE = 1,  // multiply the result by the launch's scale (fused AVG / pre-division)
   SAR_F_LOCAL = 2,  // REDUCE: the own slot is one of the addends

@@ -199,6 +199,7 @@ struct Item {
   uint32_t fidx;        // flag index
   uint64_t elem0;       // first element
   uint32_t nelem;       // elements in the tile
+  uint32_t need_ver;    // SAR_STAGE_OUT: version the own slot must have reached
 };
 
 // Geometry of the table resolved once per launch into shared memory, so that
@@ -213,6 +214,7 @@ struct RoundGeom { uint32_t op_begin, m, max_tiles, pad; };
 struct TableGeom {
   OpGeom op[SAR_MAX_OPS];
   RoundGeom round[2][SAR_MAX_ROUNDS];   // per lane
+  SarOp stage_op[2];                    // pseudo ops of staged mode: [0] SAR_STAGE_IN, [1] SAR_STAGE_OUT
   uint32_t num_rounds;
   uint32_t lanes;                       // lanes in effect for this launch (1 or 2)
   // round gating: round_prefix[R] = this rank's items in the schedule rounds before R (all lanes);
@@ -251,6 +253,12 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t n
     sar_lane_of_block(0, nblocks, table_lanes, P.lane1_eighths, &lanes, &lane, &lb, &lnb);
     G.lanes = lanes;
     G.num_rounds = nrounds;
+    for (int k = 0; k < 2; ++k) {
+      SarOp z{};
+      z.kind = k == 0 ? SAR_STAGE_IN : SAR_STAGE_OUT;
+      z.round = 255; z.parts = 1;       // outside every schedule round: neither traced nor counted by the round gate
+      G.stage_op[k] = z;
+    }
   }
   __syncthreads();
   for (uint32_t r = threadIdx.x; r < nrounds; r += blockDim.x) {
@@ -267,18 +275,26 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t n
   __syncthreads();
 }
 
-// Iterates the items of block `block` of `nblocks` in table order.
+// Iterates the items of block `block` of `nblocks` in table order.  In staged mode the table's items are
+// preceded by one stage-in item per tile of the buffer and followed by one stage-out item per tile (chunks
+// interleaved tile by tile, dealt to all blocks of the rank whatever their lane).
 struct ItemWalker {
   const SarLaunchParams* P;
   const TableGeom* G;
+  uint32_t block_all, nblocks_all;   // position and size among all blocks of the rank
   uint32_t block, nblocks;   // position and size inside the block's lane
   uint32_t lane;
   uint32_t ri;            // current round index
   uint32_t ob, m, items, k, base_mod;
+  uint32_t phase;         // 0: stage-in, 1: the table, 2: stage-out, 3: done
+  uint32_t sk;            // next staging item of this block
   __device__ void init(const SarLaunchParams* p, const TableGeom* g, uint32_t b, uint32_t nb) {
     P = p; G = g; ri = 0; base_mod = 0;
+    block_all = b; nblocks_all = nb;
     uint32_t lanes;
     sar_lane_of_block(b, nb, g->lanes, p->lane1_eighths, &lanes, &lane, &block, &nblocks);
+    phase = p->user_in ? 0u : 1u;
+    sk = block_all;
     load_round();
   }
   __device__ void load_round() {
@@ -292,26 +308,56 @@ struct ItemWalker {
       ++ri;
     }
   }
-  // false when the table is exhausted
+  // staging item sk: tile sk / num_chunks of chunk sk % num_chunks
+  __device__ bool next_staging(Item* it, uint32_t which) {
+    const uint32_t nch = P->geom.num_chunks;
+    const uint32_t total = P->geom.tiles_per_chunk * nch;
+    while (sk < total) {
+      const uint32_t c = sk % nch, lt = sk / nch;
+      sk += nblocks_all;
+      if (lt >= sar_chunk_tiles(P->geom, c)) continue;
+      const uint64_t cb = sar_chunk_begin(P->geom, c);
+      const uint64_t ce = cb + sar_chunk_len(P->geom, c);
+      const uint64_t e0 = cb + (uint64_t)lt * P->geom.tile_elems;
+      const uint64_t e1 = e0 + P->geom.tile_elems < ce ? e0 + P->geom.tile_elems : ce;
+      it->op = &G->stage_op[which]; it->tile = lt; it->fidx = sar_flag_index(P->geom, c, lt);
+      it->elem0 = e0; it->nelem = (uint32_t)(e1 - e0); it->need_ver = P->final_ver[c];
+      return true;
+    }
+    return false;
+  }
+  // false when the work list is exhausted
   __device__ bool next(Item* it) {
-    while (ri < G->num_rounds) {
-      while (k < items) {
-        const uint32_t o = ob + k % m;
-        const uint32_t lt = k / m;
-        k += nblocks;
-        const OpGeom& og = G->op[o];
-        if (lt >= og.ntiles) continue;
-        const SarOp* op = P->ops + o;
-        const uint64_t e0 = og.elem0 + (uint64_t)lt * P->geom.tile_elems;
-        uint64_t e1 = e0 + P->geom.tile_elems;
-        if (e1 > og.elem_end) e1 = og.elem_end;
-        it->op = op; it->tile = og.tile0 + lt; it->fidx = sar_flag_index(P->geom, op->chunk, og.tile0 + lt);
-        it->elem0 = e0; it->nelem = (uint32_t)(e1 - e0);
-        return true;
+    if (phase == 0) {
+      if (next_staging(it, 0)) return true;
+      phase = 1;
+    }
+    if (phase == 1) {
+      while (ri < G->num_rounds) {
+        while (k < items) {
+          const uint32_t o = ob + k % m;
+          const uint32_t lt = k / m;
+          k += nblocks;
+          const OpGeom& og = G->op[o];
+          if (lt >= og.ntiles) continue;
+          const SarOp* op = P->ops + o;
+          const uint64_t e0 = og.elem0 + (uint64_t)lt * P->geom.tile_elems;
+          uint64_t e1 = e0 + P->geom.tile_elems;
+          if (e1 > og.elem_end) e1 = og.elem_end;
+          it->op = op; it->tile = og.tile0 + lt; it->fidx = sar_flag_index(P->geom, op->chunk, og.tile0 + lt);
+          it->elem0 = e0; it->nelem = (uint32_t)(e1 - e0); it->need_ver = 0;
+          return true;
+        }
+        base_mod = (base_mod + items) % nblocks;
+        ++ri;
+        load_round();
       }
-      base_mod = (base_mod + items) % nblocks;
-      ++ri;
-      load_round();
+      phase = P->user_out ? 2u : 3u;
+      sk = block_all;
+    }
+    if (phase == 2) {
+      if (next_staging(it, 1)) return true;
+      phase = 3;
     }
     return false;
   }
@@ -396,13 +442,18 @@ __device__ __noinline__ bool wait_gate(const SarLaunchParams& P, uint32_t round,
 __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const WaitCtx& w, uint32_t* arrived_mask,
                                 uint32_t* gate_passed) {
   const SarOp* op = it.op;
+  if (op->kind == SAR_STAGE_IN) return true;   // the previous collective's exit barrier has released the slot
+  if (op->kind == SAR_STAGE_OUT)
+    return wait_word(P.comm.flags[P.rank] + it.fidx, P.epoch_base + it.need_ver, w, SAR_TIMEOUT_FLAG);
+  // staged mode: version 0 of a tile exists once its owner has copied it in, which the tile's flag tells
+  const bool staged = P.user_in != nullptr;
   if (P.gate_rounds && op->round >= 1 && op->round < SAR_GATE_ALL_DONE) {
     if (op->round > *gate_passed) {
       if (!wait_gate(P, op->round, w)) return false;
       *gate_passed = op->round;
     }
     // a full barrier between rounds: every participant has arrived and every operand is complete
-    if (P.gate_slack == 0) { *arrived_mask = P.participants; return true; }
+    if (P.gate_slack == 0 && !staged) { *arrived_mask = P.participants; return true; }
   }
   for (int q = 0; q < op->nsrc; ++q) {
     const int src = op->src[q];
@@ -410,10 +461,10 @@ __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const 
       if (!wait_word(&P.comm.ctrl[src]->arrival, P.epoch_base, w, SAR_TIMEOUT_ARRIVAL)) return false;
       *arrived_mask |= 1u << src;
     }
-    if (op->src_ver[q] && !wait_word(P.comm.flags[src] + it.fidx, P.epoch_base + op->src_ver[q], w, SAR_TIMEOUT_FLAG))
+    if ((op->src_ver[q] || staged) && !wait_word(P.comm.flags[src] + it.fidx, P.epoch_base + op->src_ver[q], w, SAR_TIMEOUT_FLAG))
       return false;
   }
-  if (op->local_ver && !wait_word(P.comm.flags[P.rank] + it.fidx, P.epoch_base + op->local_ver, w, SAR_TIMEOUT_FLAG))
+  if ((op->local_ver || staged) && !wait_word(P.comm.flags[P.rank] + it.fidx, P.epoch_base + op->local_ver, w, SAR_TIMEOUT_FLAG))
     return false;
   return true;
 }
@@ -422,6 +473,8 @@ __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const 
 // this call at system scope (fence_sys after the block barrier); the flags are
 // plain system-scope stores after that fence (release pattern).
 __device__ __forceinline__ void publish_item(const SarLaunchParams& P, const SarOp* op, uint32_t fidx) {
+  if (op->kind == SAR_STAGE_OUT) return;
+  if (op->kind == SAR_STAGE_IN) { st_relaxed_sys(P.comm.flags[P.rank] + fidx, P.epoch_base); return; }   // version 0
   if (op->kind != SAR_PUSH) st_relaxed_sys(P.comm.flags[P.rank] + fidx, P.epoch_base + op->post_ver);
   if (op->kind == SAR_REDUCE_PUSH) st_relaxed_sys(P.comm.flags[op->src[0]] + fidx, P.epoch_base + op->push_ver);
   if (op->kind == SAR_PUSH)
@@ -468,12 +521,77 @@ __device__ __forceinline__ char* mc_view_for(const SarLaunchParams& P, const Sar
   return nullptr;
 }
 
+// --------------------------------------------------------- staging (all paths)
+// Elements [e0, e0 + n) of a buffer of element type `dtype` as floats, and back.
+__device__ __forceinline__ float load_as_float(const void* base, uint64_t e, int dtype) {
+  // volatile: never served from a stale L1 line (the slot may have been written by a peer or by a bulk copy)
+  if (dtype == SAR_F32) return ((const volatile float*)base)[e];
+  const unsigned short h = ((const volatile unsigned short*)base)[e];
+  if (dtype == SAR_BF16) return __uint_as_float((uint32_t)h << 16);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+__device__ __forceinline__ void store_from_float(void* base, uint64_t e, int dtype, float v) {
+  if (dtype == SAR_F32) { ((float*)base)[e] = v; return; }
+  unsigned short h;
+  if (dtype == SAR_BF16) { __nv_bfloat16 b = __float2bfloat16_rn(v); h = *reinterpret_cast<unsigned short*>(&b); }
+  else { __half b = __float2half_rn(v); h = *reinterpret_cast<unsigned short*>(&b); }
+  ((unsigned short*)base)[e] = h;
+}
+// A staging tile: SAR_STAGE_IN copies the caller's elements into the own slot (wire type T), SAR_STAGE_OUT copies
+// the own slot into the caller's output.  Same element type and 16-byte aligned on both sides: vector copies;
+// otherwise the elements are converted one wire vector at a time.  `tid` of `nth` threads work together.
+template <typename T>
+__device__ void stage_tile(const SarLaunchParams& P, const Item& it, const uint32_t tid, const uint32_t nth) {
+  constexpr int N = Vec<T>::N;
+  const bool in = it.op->kind == SAR_STAGE_IN;
+  char* own = (char*)P.comm.buf[P.rank];
+  const int udt = P.user_dtype;
+  const bool same = udt == P.dtype;
+  const uint32_t nvec = it.nelem / N;
+  if (same) {
+    const char* src = in ? (const char*)P.user_in : own;
+    char* dst = in ? own : (char*)P.user_out;
+    const uint64_t b0 = it.elem0 * sizeof(T);
+    if ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+      uint32_t v = tid;
+      for (; v + 3 * nth < nvec; v += 4 * nth) {
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) r[u] = ld_vec_sys(src + b0 + (size_t)(v + u * nth) * 16);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) st_vec(dst + b0 + (size_t)(v + u * nth) * 16, r[u]);
+      }
+      for (; v < nvec; v += nth) st_vec(dst + b0 + (size_t)v * 16, ld_vec_sys(src + b0 + (size_t)v * 16));
+      for (uint32_t i = nvec * N + tid; i < it.nelem; i += nth)
+        store_from_float(dst, it.elem0 + i, udt, load_as_float(src, it.elem0 + i, udt));
+      return;
+    }
+  }
+  // converting (or unaligned) copy: a thread handles the N elements of one wire vector
+  const void* src = in ? P.user_in : (const void*)own;
+  void* dst = in ? (void*)own : P.user_out;
+  const int sdt = in ? udt : P.dtype, ddt = in ? P.dtype : udt;
+  for (uint32_t v = tid; v < nvec; v += nth) {
+    float f[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = load_as_float(src, it.elem0 + (uint64_t)v * N + i, sdt);
+    if (in) st_vec(own + (it.elem0 + (uint64_t)v * N) * sizeof(T), Vec<T>::pack(f));
+    else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) store_from_float(dst, it.elem0 + (uint64_t)v * N + i, ddt, f[i]);
+    }
+  }
+  for (uint32_t i = nvec * N + tid; i < it.nelem; i += nth)
+    store_from_float(dst, it.elem0 + i, ddt, load_as_float(src, it.elem0 + i, sdt));
+}
+
 // ------------------------------------------------------------------- simt path
 // `tid` of `nth` threads work on the tile together.
 template <typename T, int UNROLL>
 __device__ void simt_tile(const SarLaunchParams& P, const Item& it, const uint32_t tid, const uint32_t nth) {
   constexpr int N = Vec<T>::N;
   const SarOp* op = it.op;
+  if (op->kind >= SAR_STAGE_IN) { stage_tile<T>(P, it, tid, nth); return; }
   const uint32_t nvec = it.nelem / N;
   const uint64_t byte0 = it.elem0 * sizeof(T);
   char* own = (char*)P.comm.buf[P.rank] + byte0;
@@ -734,6 +852,8 @@ struct StageDesc {
   uint32_t fidx;
   uint32_t tail_elems;  // sub-vector tail of the item (handled with plain loads), last piece only
   uint64_t tail_elem0;
+  uint64_t item_elem0;  // staging items (executed by the consumer threads with plain loads and stores)
+  uint32_t item_elems;
 };
 struct PendEntry { const SarOp* op; uint32_t fidx; uint32_t seq; };
 
@@ -868,6 +988,17 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         if (P.trace_rounds) trace_item_start(P, it.op, t_begin, globaltimer());
         fence_proxy_async_global();   // flags were acquired through the generic proxy; the copies use the async one
         const SarOp* op = it.op;
+        if (op->kind >= SAR_STAGE_IN) {
+          // a staging tile: no bulk copy, the consumer threads move (and convert) it themselves
+          const uint32_t s = seq % nst;
+          if (!acquire_stage(s)) { ok = false; break; }
+          StageDesc& d = S.desc[s];
+          d.op = op; d.byte_off = 0; d.bytes = 0; d.slot_bytes = 0; d.nsrc_total = 0; d.fidx = it.fidx; d.last = 1u;
+          d.tail_elems = 0; d.tail_elem0 = 0; d.item_elem0 = it.elem0; d.item_elems = it.nelem;
+          mbar_arrive(&S.full[s]);
+          ++seq;
+          continue;
+        }
         const bool push_only = op->kind == SAR_PUSH;            // the only source is the own slot
         const bool local = push_only || op_reads_local(op);
         const uint32_t npeer = push_only ? 0u : op->nsrc;
@@ -940,7 +1071,11 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       if (d.op == nullptr) break;
       const SarOp* op = d.op;
       unsigned char* stage = S.ring[s];
-      if (op->kind != SAR_COPY && op->kind != SAR_PUSH && d.bytes) {
+      if (op->kind >= SAR_STAGE_IN) {
+        Item sit{};
+        sit.op = op; sit.elem0 = d.item_elem0; sit.nelem = d.item_elems;
+        stage_tile<T>(P, sit, ctid, CT);
+      } else if (op->kind != SAR_COPY && op->kind != SAR_PUSH && d.bytes) {
         const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
         const uint32_t nvec = d.bytes / 16;
         const uint32_t nsrc = d.nsrc_total;

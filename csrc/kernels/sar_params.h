@@ -42,6 +42,17 @@ struct SarLaunchParams {
   uint64_t gate_base;     // round gating: value that stands for round 0 of this launch (grows by >= 32 per launch)
   uint32_t stages;        // bulk-copy path: ring stages in use (0 or > the ring size: all)
   uint32_t store_window;  // bulk-copy path: store groups a block keeps in flight (3, 8 or 16; 0: 3)
+  // Staged mode (all three null/zero: off).  The caller's tensor is not reachable by peers: the kernel itself copies
+  // it tile by tile into this rank's buffer before the table's ops (announcing every tile as version 0 through its
+  // flag, so that nobody waits for the whole copy) and copies every tile that has reached its final version out
+  // again, converting between the caller's element type and the wire type on the way.  Every rank of the
+  // collective must run in the same mode: in staged mode version 0 of a peer's tile is waited for through the
+  // tile's flag, otherwise through the peer's arrival word.
+  const void* user_in;
+  void* user_out;
+  int32_t user_dtype;     // SarDtype of user_in / user_out
+  uint8_t final_ver[SAR_MAX_CHUNKS];   // version of this rank's slot of every chunk when the table is done
+  uint32_t pad2;
   uint64_t delay_ns;      // spin this long before arriving (a late rank when ranks share one launch)
   SarMcGroup mc[2];       // multicast views (simt path): all ranks, and e.g. the non-stragglers
 };

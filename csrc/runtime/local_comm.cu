@@ -179,6 +179,10 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
     if (err) snprintf(err, errlen, "program is for %d ranks, communicator has %d", nph ? sar_table_nranks(sar_program_phase(prog, 0)) : 0, n);
     return 1;
   }
+  if (o->user_in && o->user_out && nph != 1) {
+    if (err) snprintf(err, errlen, "staged mode serves single-phase programs");
+    return 1;
+  }
   for (int r = 0; r < n; ++r)
     if (((uintptr_t)bufs[r]) & 15) { if (err) snprintf(err, errlen, "buffer of rank %d is not 16-byte aligned", r); return 1; }
   const uint32_t esize = dtype == SAR_F32 ? 4 : 2;
@@ -251,6 +255,10 @@ int sar_local_run(sar_local_comm* c, const sar_program* prog, void* const* bufs,
           P.mc[grp].base = (char*)mc_alloc->mc[grp][r] + mc_off;
           P.mc[grp].members = mc_alloc->members[grp];
         }
+      }
+      if (o->user_in && o->user_out) {
+        P.user_in = o->user_in[r]; P.user_out = o->user_out[r]; P.user_dtype = o->user_dtype;
+        sar_table_final_ver(t, r, P.final_ver);
       }
       P.delay_ns = 0;
       if (c->emulate && delay_ns && delay_ns[r] && !delayed[r] && (parts >> r & 1)) { P.delay_ns = delay_ns[r]; delayed[r] = true; }

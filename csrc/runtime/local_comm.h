@@ -26,6 +26,12 @@ struct sar_run_opts {
   int trace_rounds;       // 1: keep per-round statistics of this run (see sar_local_round_trace)
   int stages;             // bulk-copy path: shared-memory ring stages per block (<= 0: all six)
   int store_window;       // bulk-copy path: store groups a block keeps in flight: 3, 8 or 16 (<= 0: default)
+  // Staged mode (single-phase programs): bufs[r] only serves as the buffer peers can reach; rank r's input is read
+  // from user_in[r] and its result written to user_out[r] (elements of user_dtype, converted to and from the
+  // collective's dtype) by the collective kernel itself.  NULL: off.
+  void* const* user_in;
+  void* const* user_out;
+  int user_dtype;
 };
 
 // devices[r] is the CUDA device of rank r.  emulate != 0 places every rank on

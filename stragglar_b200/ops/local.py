@@ -22,7 +22,8 @@ PATHS = {"simt": 0, "tma": 1, "simta": 2}
 class RunOpts(C.Structure):
     _fields_ = [("path", C.c_int), ("blocks", C.c_int), ("threads", C.c_int), ("tile_bytes", C.c_uint32),
                 ("timeout_s", C.c_double), ("scale", C.c_float), ("timed", C.c_int), ("trace_rounds", C.c_int),
-                ("stages", C.c_int), ("store_window", C.c_int)]
+                ("stages", C.c_int), ("store_window", C.c_int),
+                ("user_in", C.POINTER(C.c_void_p)), ("user_out", C.POINTER(C.c_void_p)), ("user_dtype", C.c_int)]
 
 
 def cuda_lib():
@@ -144,9 +145,14 @@ class LocalComm:
 
     def run(self, program: Program, tensors, path: str = "simt", blocks: int = 0, threads: int = 0,
             tile_bytes: int = 0, scale: float = 1.0, delay_ms: Optional[Sequence[float]] = None,
-            timeout_s: float = 10.0, timed: bool = False, trace_rounds: bool = False, stages: int = 0, store_window: int = 0) -> None:
+            timeout_s: float = 10.0, timed: bool = False, trace_rounds: bool = False, stages: int = 0, store_window: int = 0,
+            user_tensors=None) -> None:
         """Enqueue ``program`` in place on ``tensors`` (one per rank).  ``trace_rounds`` keeps per-round
-        statistics of this run for :meth:`round_trace`."""
+        statistics of this run for :meth:`round_trace`.
+
+        ``user_tensors`` (one per rank, any of the three dtypes, same numel) selects staged mode for a single-phase
+        program: ``tensors`` then only serve as the buffers the ranks reach into; the kernel reads rank r's input
+        from ``user_tensors[r]`` and writes the result back there, converting between the two dtypes."""
         if len(tensors) != self.n:
             raise ValueError(f"need {self.n} tensors")
         t0 = tensors[0]
@@ -157,7 +163,15 @@ class LocalComm:
             raise ValueError("program was freed")
         # program handles come from libsar_core.so; libsar_cuda.so is built from the same
         # sources and reads them through the same accessors
-        opts = RunOpts(PATHS[path], blocks, threads, tile_bytes, timeout_s, scale, int(timed), int(trace_rounds), stages, store_window)
+        uin = None
+        udt = 0
+        if user_tensors is not None:
+            if len(user_tensors) != self.n or any(u.numel() != t0.numel() or not u.is_contiguous() for u in user_tensors):
+                raise ValueError("user_tensors: one contiguous tensor of the same numel per rank")
+            uin = (C.c_void_p * self.n)(*[u.data_ptr() for u in user_tensors])
+            udt = _dtype_code(user_tensors[0])
+        opts = RunOpts(PATHS[path], blocks, threads, tile_bytes, timeout_s, scale, int(timed), int(trace_rounds), stages,
+                       store_window, uin, uin, udt)
         ptrs = (C.c_void_p * self.n)(*[t.data_ptr() for t in tensors])
         dl = (C.c_uint64 * self.n)(*[int(d * 1e6) for d in delay_ms]) if delay_ms is not None else None
         err = C.create_string_buffer(256)

@@ -247,3 +247,35 @@ def test_round_gating(alg, n, slack, path, monkeypatch):
     if slack == 0:
         assert all(ends[a] <= starts[b] for a, b in zip(rounds, rounds[1:])), (starts, ends)
     comm.close()
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("alg,n", [("stragglar", 8), ("ring", 4), ("rsag", 4), ("stragglar_a2a", 6), ("stragglar", 1)])
+@pytest.mark.parametrize("wire,user", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                       (torch.float32, torch.bfloat16)])
+def test_staged_mode_reads_and_writes_the_callers_tensors(alg, n, wire, user, path):
+    """Staged mode: the kernel itself copies the caller's tensor into the buffer peers reach (converting to the wire
+    dtype), runs the table and copies every finished tile back; no separate copy or cast kernels."""
+    from stragglar_b200 import ops
+    count = 70_001
+    comm = ops.LocalComm(n, emulate=True)
+    prog = sc.compile_program(alg, n)
+    if len(prog.phases) != 1:
+        pytest.skip("staged mode serves single-phase programs")
+    users = _inputs(n, count, user)
+    # what the wire carries: the inputs rounded to the wire dtype, summed in fp32
+    want = torch.stack([u.to(wire).double() for u in users]).sum(0) * 0.5
+    arena = [torch.full((count,), float("nan"), dtype=wire, device="cuda:0") for _ in range(n)]
+    torch.cuda.synchronize()
+    for rep in range(2):   # twice: the second run finds the flags of the first
+        if rep:
+            for u, v in zip(users, _inputs(n, count, user)):
+                u.copy_(v)
+            torch.cuda.synchronize()
+        comm.run(prog, arena, path=path, blocks=3, tile_bytes=4096, scale=0.5, timeout_s=5.0, user_tensors=users)
+        comm.sync()
+        lo = torch.bfloat16 in (wire, user)
+        tol = dict(atol=6e-2, rtol=2e-2) if lo else dict(atol=1e-5, rtol=1e-6)
+        for u in users:
+            torch.testing.assert_close(u.double(), want, **tol)
+    comm.close()
