@@ -310,7 +310,7 @@ void ProcessGroupStragglar::device_barrier(Side& s) {
 }
 
 void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_t data_off, uint64_t count,
-                                        at::ScalarType dtype, float scale) {
+                                        at::ScalarType dtype, float scale, void* user, int user_dtype) {
   Transport& t = *s.t;
   const int n = getSize(), me = getRank();
   const int dt = dtype_code(dtype);
@@ -356,6 +356,11 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.epoch_base = epoch; P.scale = scale; P.dtype = dt;
       P.timeout_ns = (uint64_t)(opts_.timeout_s * 1e9);
       P.status = t.status(); P.trace = t.trace_words(); P.delay_ns = 0;
+      if (user) {
+        // staged mode: the kernel copies the caller's tensor in and out itself (see sar_params.h)
+        P.user_in = user; P.user_out = user; P.user_dtype = user_dtype;
+        for (size_t ch = 0; ch < rt.final_ver.size() && ch < SAR_MAX_CHUNKS; ++ch) P.final_ver[ch] = rt.final_ver[ch];
+      }
       P.gate_rounds = gated ? 1u : 0u;
       P.gate_base = epoch64; P.gate_slack = sar::gate_slack(g.tiles_per_chunk);
       P.stages = (uint32_t)c.stages_hint;
@@ -434,6 +439,16 @@ void ProcessGroupStragglar::allreduce_impl(Side& s, at::Tensor& tensor, float sc
   piece = piece / 256 * 256;
   TORCH_CHECK(piece > 0, "staging area too small");
   char* stage = t.data(getRank()) + t.staging_off();
+  if (t.cuda() && prog.phases.size() == 1) {
+    // Any other CUDA tensor (a DDP bucket, say): the staging area only serves the peers.  One kernel per piece
+    // copies the tensor in tile by tile (casting to the communication dtype), reduces, and copies every finished
+    // tile back (casting again); no separate copy or cast launches.  Every rank must pass the same kind of tensor.
+    for (uint64_t off = 0; off < count; off += piece) {
+      const uint64_t k = std::min<uint64_t>(piece, count - off);
+      run_program(s, prog, t.staging_off(), k, cdt, scale, ptr + off * tsize, dtype_code(tdt));
+    }
+    return;
+  }
   for (uint64_t off = 0; off < count; off += piece) {
     const uint64_t k = std::min<uint64_t>(piece, count - off);
     if (cdt == tdt) copy_local(s, stage, ptr + off * tsize, k * tsize);

@@ -162,7 +162,10 @@ class ProcessGroupStragglar : public c10d::Backend {
   Side& side(const at::Tensor& like);
   Side& side(bool cuda, int device);
   const sar::Program& program(size_t bytes = 0);
-  void run_program(Side& s, const sar::Program& prog, size_t data_off, uint64_t count, at::ScalarType dtype, float scale);
+  // `user` (CUDA, single-phase programs): staged mode -- the kernel reads the input from and writes the result to
+  // `user` (elements of SarDtype `user_dtype`), the arena range at data_off only serves the peers
+  void run_program(Side& s, const sar::Program& prog, size_t data_off, uint64_t count, at::ScalarType dtype, float scale,
+                   void* user = nullptr, int user_dtype = 0);
   void device_barrier(Side& s);
   c10::intrusive_ptr<WorkStragglar> begin(Side& s, c10d::OpType op, std::vector<at::Tensor> outputs);
   void finish(Side& s, const c10::intrusive_ptr<WorkStragglar>& w);

@@ -153,7 +153,7 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o_in, con
   const bool is_sar = !strncmp(alg, "stragglar", 9);
 
   if (header)
-    printf("algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s),n,dtype,path,time_us_max,algbw_GBps,busbw_GBps,roofline_frac,real_delay_ms\n");
+    printf("algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s),n,dtype,path,time_us_max,algbw_GBps,busbw_GBps,roofline_frac,real_delay_ms,kernel_us_max\n");
   int failures = 0;
   std::vector<float> ms(n);
   for (int iter = -o.warmup; iter < numIters; ++iter) {
@@ -230,8 +230,15 @@ static int run_config(sar_local_comm* comm, Buffers& B, const Options& o_in, con
     const double algbw = (double)bytes / 1e9 / (net_ms / 1e3);
     const double busbw = algbw * 2.0 * (n - 1) / std::max(n, 1);
     const double roof_ms = link_bytes / (link_gbs * 1e9) * 1e3;
-    printf("%s,%zu,%d,%.3f,%.3f,%.3f,%d,%s,%s,%.1f,%.2f,%.2f,%.3f,%.3f\n", label, (size_t)count * esize, iter + 1, sleepTime, t, bw, n,
-           dtype_name(o.dtype), path_label(o.path, B.mc_groups), t * 1e3, algbw, busbw, net_ms > 0 ? roof_ms / net_ms : 0.0, real_delay_ms);
+    // inside the kernels: from a rank's arrival to its exit (its last phase), longest over the ranks
+    double kernel_us = 0;
+    {
+      std::vector<uint64_t> tr(2 * (size_t)n);
+      if (!sar_local_trace(comm, tr.data()))
+        for (int r = 0; r < n; ++r) if (tr[2 * r + 1] > tr[2 * r]) kernel_us = std::max(kernel_us, (tr[2 * r + 1] - tr[2 * r]) / 1e3);
+    }
+    printf("%s,%zu,%d,%.3f,%.3f,%.3f,%d,%s,%s,%.1f,%.2f,%.2f,%.3f,%.3f,%.1f\n", label, (size_t)count * esize, iter + 1, sleepTime, t, bw, n,
+           dtype_name(o.dtype), path_label(o.path, B.mc_groups), t * 1e3, algbw, busbw, net_ms > 0 ? roof_ms / net_ms : 0.0, real_delay_ms, kernel_us);
   }
   sar_program_free(prog);
   if (post) sar_program_free(post);

@@ -107,8 +107,13 @@ struct SarCtrl {
   // round before R.  64-bit and raised with a max-reduction: announcements of different rounds may
   // overtake one another on the way, and the value never wraps.
   uint64_t gate[SAR_MAX_RANKS];
+  // Mirrors, written by the other ranks into THIS rank's memory so that waiting polls local memory instead of
+  // crossing the link once per peer: arrival_m[q] / exited_m[q] = rank q's `arrival` / `exited` word.  The CUDA
+  // kernels write and read the mirrors; the host executor, whose ranks share host memory, reads the words themselves.
+  uint32_t arrival_m[SAR_MAX_RANKS];
+  uint32_t exited_m[SAR_MAX_RANKS];
 };
-static_assert(sizeof(SarCtrl) == 256, "SarCtrl layout");
+static_assert(sizeof(SarCtrl) == 384, "SarCtrl layout");
 #define SAR_CTRL_WORDS (sizeof(SarCtrl) / 4)
 // Round gating.  The rounds of a matching-based schedule are contention-free one at a time: in
 // every round a rank sends at most one chunk and receives at most one.  When the rounds overlap

@@ -218,8 +218,9 @@ extern "C" {
 
 int sar_cuda_default_blocks(int path) { return path == SAR_PATH_TMA ? 32 : 64; }
 int sar_cuda_pick_blocks(int path, uint64_t bytes) {
-  const uint64_t b = bytes / (2ull << 20);
-  const int lo = 16, hi = 128;
+  // 8 x B200: 16 blocks cost 20-30 % at 16-64 MiB (0.132 ms against 0.104 at 16 MiB), 32 or more are level
+  const uint64_t b = bytes / (1ull << 20);
+  const int lo = 32, hi = 128;
   (void)path;
   return (int)(b < (uint64_t)lo ? lo : (b > (uint64_t)hi ? hi : b));
 }

@@ -192,6 +192,29 @@ __device__ __noinline__ bool wait_word(const uint32_t* p, uint32_t target, const
   }
 }
 
+// Waits until the mirror word of every rank in `mask` (arrival_m or exited_m in this rank's own memory) has
+// reached `target`.  All words are read at once, so a wait for seven peers costs one local round trip, not seven
+// trips over the link.  Returns the ranks that have not got there (0 = all there); failure recorded.
+__device__ __noinline__ uint32_t wait_mirrors(const uint32_t* words, uint32_t mask, int nranks, uint32_t target, const WaitCtx& w,
+                                              uint32_t fail_code) {
+  uint32_t ns = 20;
+  for (uint64_t it = 0;; ++it) {
+    uint32_t v[SAR_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < SAR_MAX_RANKS; ++r) v[r] = (r < nranks && (mask >> r & 1)) ? ld_relaxed_sys(words + r) : target;
+    uint32_t missing = 0;
+#pragma unroll
+    for (int r = 0; r < SAR_MAX_RANKS; ++r) if (!sar_reached(v[r], target)) missing |= 1u << r;
+    if (!missing) { fence_sys(); return 0; }   // acquire: what the announcers wrote before is visible now
+    if ((it & 15) == 15) {
+      if (*(volatile uint32_t*)w.abort_flag) return missing;
+      if (globaltimer() > w.deadline) { record_failure(w, fail_code); return missing; }
+    }
+    __nanosleep(ns);
+    if (ns < 400) ns += ns >> 1;
+  }
+}
+
 // An item of the rank's work list, resolved against the geometry.
 struct Item {
   const SarOp* op;
@@ -455,12 +478,17 @@ __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const 
     // a full barrier between rounds: every participant has arrived and every operand is complete
     if (P.gate_slack == 0 && !staged) { *arrived_mask = P.participants; return true; }
   }
+  {
+    uint32_t need = 0;
+    for (int q = 0; q < op->nsrc; ++q) need |= 1u << op->src[q];
+    need &= ~*arrived_mask;
+    if (need) {
+      if (wait_mirrors(P.comm.ctrl[P.rank]->arrival_m, need, P.nranks, P.epoch_base, w, SAR_TIMEOUT_ARRIVAL)) return false;
+      *arrived_mask |= need;
+    }
+  }
   for (int q = 0; q < op->nsrc; ++q) {
     const int src = op->src[q];
-    if (!(*arrived_mask >> src & 1)) {
-      if (!wait_word(&P.comm.ctrl[src]->arrival, P.epoch_base, w, SAR_TIMEOUT_ARRIVAL)) return false;
-      *arrived_mask |= 1u << src;
-    }
     if ((op->src_ver[q] || staged) && !wait_word(P.comm.flags[src] + it.fidx, P.epoch_base + op->src_ver[q], w, SAR_TIMEOUT_FLAG))
       return false;
   }
@@ -762,6 +790,9 @@ __device__ __forceinline__ WaitCtx enter_collective(const SarLaunchParams& P, ui
   if (block == 0 && threadIdx.x == 0) {
     if (P.trace) P.trace[0] = globaltimer();
     st_release_sys(&P.comm.ctrl[P.rank]->arrival, P.epoch_base);
+    // the same word into every participant's memory, where its waits look for it
+    for (int q = 0; q < P.nranks; ++q)
+      if (q != P.rank && (P.participants >> q & 1)) st_relaxed_sys(&P.comm.ctrl[q]->arrival_m[P.rank], P.epoch_base);
   }
   return w;
 }
@@ -782,10 +813,9 @@ __device__ void leave_collective(const SarLaunchParams& P, const WaitCtx& w, uin
   if (*(volatile uint32_t*)w.abort_flag == 0) {
     fence_sys();
     st_release_sys(&me->exited, P.epoch_base);
-    for (int r = 0; r < P.nranks; ++r) {
-      if (r == P.rank || !(P.participants >> r & 1)) continue;
-      if (!wait_word(&P.comm.ctrl[r]->exited, P.epoch_base, w, SAR_TIMEOUT_EXIT)) break;
-    }
+    for (int q = 0; q < P.nranks; ++q)
+      if (q != P.rank && (P.participants >> q & 1)) st_relaxed_sys(&P.comm.ctrl[q]->exited_m[P.rank], P.epoch_base);
+    wait_mirrors(me->exited_m, P.participants & ~(1u << P.rank), P.nranks, P.epoch_base, w, SAR_TIMEOUT_EXIT);
   } else if (P.status) {
     atomicCAS(P.status, 0u, (uint32_t)SAR_ABORTED);
   }

@@ -189,9 +189,10 @@ def fused_avg_hook(state, bucket):
 
 
 def bf16_fused_avg_hook(state, bucket):
-    """DDP communication hook: gradients travel as bfloat16.  The cast (and the
-    division by world_size) happen inside the staging pass and the kernel, not
-    as separate elementwise launches."""
+    """DDP communication hook: gradients travel as bfloat16.  One kernel per bucket reads the fp32 bucket tile by
+    tile, converts it to bfloat16 into the buffer the peers reach, reduces (fp32 accumulation, the division by
+    world_size applied to the final sums) and writes every finished tile back to the bucket as fp32; there are no
+    separate cast or copy launches."""
     import torch
     buf = bucket.buffer()
     work = all_reduce_ex(buf, average=True, comm_dtype=torch.bfloat16, group=state)

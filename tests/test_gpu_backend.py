@@ -43,9 +43,17 @@ def _cuda_collectives(rank, world):
     dist.all_reduce(s, op=dist.ReduceOp.AVG)
     torch.testing.assert_close(s.double(), want / world, atol=2e-5, rtol=1e-6)
     sp.set_straggler(-1)
-    # bf16 through the staging cast
+    # an ordinary tensor (not in the symmetric heap) costs exactly one kernel: copy-in, reduction and copy-out are fused
+    y = x.clone()
+    l0 = sp.launches(dev)
+    dist.all_reduce(y)
+    assert sp.launches(dev) - l0 == 1
+    torch.testing.assert_close(y.double(), want, atol=2e-5, rtol=1e-6)
+    # bf16 on the wire, fp32 at the caller: the casts and the average are in the same single kernel
     z = x.clone()
+    l0 = sp.launches(dev)
     sp.all_reduce_ex(z, average=True, comm_dtype=torch.bfloat16).wait()
+    assert sp.launches(dev) - l0 == 1
     torch.testing.assert_close(z.double(), want / world, atol=4e-2, rtol=2e-2)
     h = _seeded(rank, 4099, torch.bfloat16, dev)
     wh = torch.stack([_seeded(r, 4099, torch.bfloat16).double() for r in range(world)]).sum(0).to(dev)
