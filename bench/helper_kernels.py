@@ -54,8 +54,8 @@ def main() -> int:
         ("sar_fill_uniform_kernel<float>", 4 * n, lambda: L.sar_cuda_fill_uniform(f32.data_ptr(), n, 0, 3, st)),
         ("sar_fill_uniform_kernel<float> (2nd buffer)", 4 * n, lambda: L.sar_cuda_fill_uniform(f32b.data_ptr(), n, 0, 4, st)),
         ("sar_fill_const_kernel<bf16>", 2 * n, lambda: L.sar_cuda_fill_const(bf.data_ptr(), n, 1, 1.5, st)),
-        ("sar_scale_cast_kernel<bf16,float>", 6 * n, lambda: L.sar_cuda_scale_cast(bf.data_ptr(), 1, f32.data_ptr(), 0, n, 0.125, st)),
-        ("sar_reduce_segments_kernel<float>", 12 * n, lambda: L.sar_cuda_reduce_segments(f32c.data_ptr(), srcs, 2, n, 0, 1.0, st)),
+        ("sar_scale_cast_vec8_kernel<bf16,float>", 6 * n, lambda: L.sar_cuda_scale_cast(bf.data_ptr(), 1, f32.data_ptr(), 0, n, 0.125, st)),
+        ("sar_reduce_segments_vec_kernel<float>", 12 * n, lambda: L.sar_cuda_reduce_segments(f32c.data_ptr(), srcs, 2, n, 0, 1.0, st)),
         ("sar_verify_kernel<float>", 4 * n, lambda: L.sar_cuda_verify_uniform_sum(f32c.data_ptr(), 0, n, 0, seeds, 2, 1.0, 1e-5, 0.0, res.data_ptr(), st)),
         ("sar_scale_vec_kernel<float>", 8 * n, lambda: L.sar_cuda_scale_cast(f32c.data_ptr(), 0, f32c.data_ptr(), 0, n, 0.5, st)),
         ("sar_copy_segments_kernel", 8 * n, lambda: L.sar_cuda_copy_segments(seg, 1, st)),

@@ -1,7 +1,7 @@
 #!/usr/bin/env bash
 # The full AllReduce comparison on one 8-GPU box:
 # this library (bin/allreduce), the unmodified reference programs (baseline/_ref)
-# and stock NCCL (bench/nccl_allreduce.py).  CSVs and a summary land in $OUT.
+# and stock NCCL (bench/backend_allreduce.py).  CSVs and a summary land in $OUT.
 #
 #   bench/sweep.sh [out_dir]        # needs: python -m stragglar_b200.build ; baseline/build_reference.sh <reference checkout>
 set -u
@@ -36,9 +36,9 @@ fi
 
 # stock NCCL, 8 and 6 ranks
 python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29601 \
-  bench/nccl_allreduce.py --sizes $SZ --delays=-1,1,5,10 --iters $IT --warmup $W > "$OUT/nccl_n8.csv" 2> "$OUT/nccl_n8.err"
+  bench/backend_allreduce.py --sizes $SZ --delays=-1,1,5,10 --iters $IT --warmup $W > "$OUT/nccl_n8.csv" 2> "$OUT/nccl_n8.err"
 python -m torch.distributed.run --nnodes=1 --nproc-per-node 6 --master-addr 127.0.0.1 --master-port 29602 \
-  bench/nccl_allreduce.py --sizes 16777216,268435456,1073741824 --delays=5 --iters $IT --warmup $W > "$OUT/nccl_n6.csv" 2> "$OUT/nccl_n6.err"
+  bench/backend_allreduce.py --sizes 16777216,268435456,1073741824 --delays=5 --iters $IT --warmup $W > "$OUT/nccl_n6.csv" 2> "$OUT/nccl_n6.err"
 python -m torch.distributed.run --nnodes=1 --nproc-per-node 6 --master-addr 127.0.0.1 --master-port 29603 \
   bench/sendrecv_allreduce.py --alg stragglar --sizes 16777216,268435456,1073741824 --delays=5 --iters 10 --warmup 3 > "$OUT/sendrecv_n6.csv" 2> "$OUT/sendrecv_n6.err"
 

@@ -126,6 +126,28 @@ __global__ void sar_scale_cast_kernel(TD* dst, const TS* src, uint64_t count, fl
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x)
     dst[i] = from_float<TD>(to_float(src[i]) * scale);
 }
+// converting fast path: eight elements per thread and turn, 16-byte accesses on the 2-byte side and 2 x 16 bytes
+// on the 4-byte side (both pointers 16-byte aligned)
+template <typename TD, typename TS>
+__global__ void sar_scale_cast_vec8_kernel(TD* dst, const TS* src, uint64_t ngroups, float scale) {
+  for (uint64_t g = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; g < ngroups; g += (uint64_t)gridDim.x * blockDim.x) {
+    float f[8];
+    if constexpr (sizeof(TS) == 4) {
+      const float4 a = reinterpret_cast<const float4*>(src)[2 * g], b = reinterpret_cast<const float4*>(src)[2 * g + 1];
+      f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+      Vec<TS>::unpack(reinterpret_cast<const uint4*>(src)[g], f);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] *= scale;
+    if constexpr (sizeof(TD) == 4) {
+      reinterpret_cast<float4*>(dst)[2 * g] = make_float4(f[0], f[1], f[2], f[3]);
+      reinterpret_cast<float4*>(dst)[2 * g + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    } else {
+      reinterpret_cast<uint4*>(dst)[g] = Vec<TD>::pack(f);
+    }
+  }
+}
 // same-type fast path: 16 bytes per thread
 template <typename T>
 __global__ void sar_scale_vec_kernel(uint4* dst, const uint4* src, uint64_t nvec, float scale) {
@@ -187,11 +209,30 @@ __global__ void sar_copy_segments_kernel(SegList L) {
 }
 struct SrcList { const void* p[SAR_MAX_RANKS]; int n; };
 template <typename T>
-__global__ void sar_reduce_segments_kernel(T* dst, SrcList L, uint64_t count, float scale) {
-  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
+__global__ void sar_reduce_segments_kernel(T* dst, SrcList L, uint64_t begin, uint64_t count, float scale) {
+  for (uint64_t i = begin + blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < L.n; ++k) acc += Vec<T>::load1((const char*)L.p[k] + i * sizeof(T));
     dst[i] = from_float<T>(acc * scale);
+  }
+}
+// 16 bytes per thread and source (all pointers 16-byte aligned); the sources may be peer memory
+template <typename T>
+__global__ void sar_reduce_segments_vec_kernel(uint4* dst, SrcList L, uint64_t nvec, float scale) {
+  constexpr int N = Vec<T>::N;
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < nvec; i += (uint64_t)gridDim.x * blockDim.x) {
+    float acc[N];
+#pragma unroll
+    for (int k = 0; k < N; ++k) acc[k] = 0.f;
+    for (int s = 0; s < L.n; ++s) {
+      float f[N];
+      Vec<T>::unpack(ld_vec_sys((const char*)L.p[s] + i * 16), f);
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] += f[k];
+    }
+#pragma unroll
+    for (int k = 0; k < N; ++k) acc[k] *= scale;
+    dst[i] = Vec<T>::pack(acc);
   }
 }
 
@@ -345,7 +386,12 @@ int sar_cuda_scale_cast(void* dst, int dst_dtype, const void* src, int src_dtype
     using TD = decltype(dtag);
     return with_dtype(src_dtype, [&](auto stag) -> int {
       using TS = decltype(stag);
-      sar_scale_cast_kernel<TD, TS><<<grid_for(count, 256), 256, 0, st>>>((TD*)dst, (const TS*)src, count, scale);
+      const bool aligned = (((uintptr_t)dst | (uintptr_t)src) & 15) == 0;
+      const uint64_t groups = aligned ? count / 8 : 0;
+      if (groups) sar_scale_cast_vec8_kernel<TD, TS><<<grid_for(groups, 256), 256, 0, st>>>((TD*)dst, (const TS*)src, groups, scale);
+      const uint64_t done = groups * 8;
+      if (done < count)
+        sar_scale_cast_kernel<TD, TS><<<grid_for(count - done, 256), 256, 0, st>>>((TD*)dst + done, (const TS*)src + done, count - done, scale);
       return (int)cudaGetLastError();
     });
   });
@@ -388,7 +434,13 @@ int sar_cuda_reduce_segments(void* dst, const void* const* srcs, int nsrc, uint6
   for (int i = 0; i < nsrc; ++i) L.p[i] = srcs[i];
   return with_dtype(dtype, [&](auto tag) -> int {
     using T = decltype(tag);
-    sar_reduce_segments_kernel<T><<<grid_for(count, 256), 256, 0, (cudaStream_t)stream>>>((T*)dst, L, count, scale);
+    bool aligned = (((uintptr_t)dst) & 15) == 0;
+    for (int i = 0; i < nsrc; ++i) aligned = aligned && (((uintptr_t)srcs[i]) & 15) == 0;
+    const uint64_t nvec = aligned ? count / Vec<T>::N : 0;
+    if (nvec) sar_reduce_segments_vec_kernel<T><<<grid_for(nvec, 256), 256, 0, (cudaStream_t)stream>>>((uint4*)dst, L, nvec, scale);
+    const uint64_t done = nvec * Vec<T>::N;
+    if (done < count)
+      sar_reduce_segments_kernel<T><<<grid_for(count - done, 256), 256, 0, (cudaStream_t)stream>>>((T*)dst, L, done, count, scale);
     return (int)cudaGetLastError();
   });
 }

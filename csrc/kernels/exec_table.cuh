@@ -882,8 +882,14 @@ struct StageDesc {
   uint32_t fidx;
   uint32_t tail_elems;  // sub-vector tail of the item (handled with plain loads), last piece only
   uint64_t tail_elem0;
-  uint64_t item_elem0;  // staging items (executed by the consumer threads with plain loads and stores)
+  // staging pieces: bulk-loaded from the caller's tensor (stage-in) or the own slot (stage-out), converted in
+  // shared memory when the element types differ, bulk-stored to the other side.  item_elems != 0: the unaligned
+  // fallback, the consumer threads move the whole item with plain loads and stores.
+  uint64_t item_elem0;
   uint32_t item_elems;
+  uint32_t dst_bytes;   // bytes stored (differs from `bytes` when the piece is converted)
+  uint64_t dst_off;     // byte offset on the destination side
+  uint32_t piece_elems; // elements in this piece
 };
 struct PendEntry { const SarOp* op; uint32_t fidx; uint32_t seq; };
 
@@ -1019,14 +1025,47 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         fence_proxy_async_global();   // flags were acquired through the generic proxy; the copies use the async one
         const SarOp* op = it.op;
         if (op->kind >= SAR_STAGE_IN) {
-          // a staging tile: no bulk copy, the consumer threads move (and convert) it themselves
-          const uint32_t s = seq % nst;
-          if (!acquire_stage(s)) { ok = false; break; }
-          StageDesc& d = S.desc[s];
-          d.op = op; d.byte_off = 0; d.bytes = 0; d.slot_bytes = 0; d.nsrc_total = 0; d.fidx = it.fidx; d.last = 1u;
-          d.tail_elems = 0; d.tail_elem0 = 0; d.item_elem0 = it.elem0; d.item_elems = it.nelem;
-          mbar_arrive(&S.full[s]);
-          ++seq;
+          const bool in = op->kind == SAR_STAGE_IN;
+          const int sdt = in ? P.user_dtype : P.dtype, ddt = in ? P.dtype : P.user_dtype;
+          const uint32_t ssz = sdt == SAR_F32 ? 4u : 2u, dsz = ddt == SAR_F32 ? 4u : 2u;
+          const char* src = in ? (const char*)P.user_in : (const char*)P.comm.buf[P.rank];
+          if (((((uintptr_t)P.user_in | (uintptr_t)P.user_out) & 15) != 0) || (((it.elem0 * ssz) | (it.elem0 * dsz)) & 15) != 0) {
+            // a caller's tensor, or a tile start, that bulk copies cannot address (they need 16-byte alignment on
+            // both sides): the consumer threads move (and convert) the tile with plain loads and stores
+            const uint32_t s = seq % nst;
+            if (!acquire_stage(s)) { ok = false; break; }
+            StageDesc& d = S.desc[s];
+            d.op = op; d.byte_off = 0; d.bytes = 0; d.slot_bytes = 0; d.nsrc_total = 0; d.fidx = it.fidx; d.last = 1u;
+            d.tail_elems = 0; d.tail_elem0 = 0; d.item_elem0 = it.elem0; d.item_elems = it.nelem; d.dst_bytes = 0;
+            mbar_arrive(&S.full[s]);
+            ++seq;
+            continue;
+          }
+          // pieces of whole 16-byte vectors on both sides (8 elements); a converted piece uses half a stage per side
+          const uint32_t big = ssz > dsz ? ssz : dsz;
+          const uint32_t piece = sdt == ddt ? (uint32_t)kStageBytes / ssz : (uint32_t)(kStageBytes / 2) / big;
+          const uint32_t body = it.nelem & ~7u, tail = it.nelem & 7u;
+          uint32_t done = 0;
+          do {
+            const uint32_t pe = body - done < piece ? body - done : piece;
+            const uint32_t s = seq % nst;
+            if (!acquire_stage(s)) { ok = false; break; }
+            StageDesc& d = S.desc[s];
+            d.op = op; d.byte_off = (it.elem0 + done) * ssz; d.bytes = pe * ssz; d.slot_bytes = 0; d.nsrc_total = 1;
+            d.dst_off = (it.elem0 + done) * dsz; d.dst_bytes = pe * dsz; d.piece_elems = pe; d.fidx = it.fidx;
+            d.item_elems = 0; d.item_elem0 = 0;
+            d.last = (done + pe >= body) ? 1u : 0u;
+            d.tail_elems = d.last ? tail : 0u;
+            d.tail_elem0 = it.elem0 + body;
+            if (pe) {
+              mbar_arrive_expect_tx(&S.full[s], d.bytes);
+              bulk_load(&S.ring[s][0], src + d.byte_off, d.bytes, &S.full[s]);
+            } else {
+              mbar_arrive(&S.full[s]);
+            }
+            ++seq;
+            done += pe;
+          } while (done < body);
           continue;
         }
         const bool push_only = op->kind == SAR_PUSH;            // the only source is the own slot
@@ -1102,9 +1141,33 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       const SarOp* op = d.op;
       unsigned char* stage = S.ring[s];
       if (op->kind >= SAR_STAGE_IN) {
-        Item sit{};
-        sit.op = op; sit.elem0 = d.item_elem0; sit.nelem = d.item_elems;
-        stage_tile<T>(P, sit, ctid, CT);
+        if (d.item_elems) {
+          Item sit{};
+          sit.op = op; sit.elem0 = d.item_elem0; sit.nelem = d.item_elems;
+          stage_tile<T>(P, sit, ctid, CT);
+        } else if (d.bytes != d.dst_bytes) {
+          // convert the piece from the first half of the stage into the second, eight elements per thread and turn
+          const bool in = op->kind == SAR_STAGE_IN;
+          const int sdt = in ? P.user_dtype : P.dtype, ddt = in ? P.dtype : P.user_dtype;
+          unsigned char* out = stage + kStageBytes / 2;
+          for (uint32_t g = ctid; g < d.piece_elems / 8; g += CT) {
+            float f[8];
+            if (sdt == SAR_F32) {
+              const float4 a = *reinterpret_cast<const float4*>(stage + (size_t)g * 32), b = *reinterpret_cast<const float4*>(stage + (size_t)g * 32 + 16);
+              f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+            } else {
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + (size_t)g * 16);
+              if (sdt == SAR_BF16) Vec<__nv_bfloat16>::unpack(v, f); else Vec<__half>::unpack(v, f);
+            }
+            if (ddt == SAR_F32) {
+              *reinterpret_cast<float4*>(out + (size_t)g * 32) = make_float4(f[0], f[1], f[2], f[3]);
+              *reinterpret_cast<float4*>(out + (size_t)g * 32 + 16) = make_float4(f[4], f[5], f[6], f[7]);
+            } else {
+              *reinterpret_cast<uint4*>(out + (size_t)g * 16) = ddt == SAR_BF16 ? Vec<__nv_bfloat16>::pack(f) : Vec<__half>::pack(f);
+            }
+          }
+          fence_proxy_async_smem();
+        }
       } else if (op->kind != SAR_COPY && op->kind != SAR_PUSH && d.bytes) {
         const float scale = (op->flags & SAR_F_SCALE) ? P.scale : 1.0f;
         const uint32_t nvec = d.bytes / 16;
@@ -1149,7 +1212,12 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
       // (a fortiori) with the previous piece's stage, which is released below.
       consumer_bar();
       if (ctid == 0) {
-        if (d.bytes) {
+        if (op->kind >= SAR_STAGE_IN) {
+          if (d.dst_bytes) {
+            char* dst = op->kind == SAR_STAGE_IN ? (char*)P.comm.buf[P.rank] : (char*)P.user_out;
+            bulk_store(dst + d.dst_off, d.bytes != d.dst_bytes ? stage + kStageBytes / 2 : stage, d.dst_bytes);
+          }
+        } else if (d.bytes) {
           if (op->kind != SAR_PUSH) bulk_store((char*)P.comm.buf[P.rank] + d.byte_off, stage, d.bytes);
           if (op->kind == SAR_REDUCE_PUSH) bulk_store((char*)P.comm.buf[op->src[0]] + d.byte_off, stage, d.bytes);
           if (op->kind == SAR_PUSH)
@@ -1157,7 +1225,14 @@ __device__ void run_rank_tma(const SarLaunchParams& P, uint32_t block, uint32_t 
         }
         bulk_commit();          // one group per piece (possibly empty), so group numbers follow seq
         if (d.last) {
-          if (d.tail_elems) { scalar_elems<T>(P, op, d.tail_elem0, d.tail_elems); __threadfence_system(); }
+          if (d.tail_elems && op->kind >= SAR_STAGE_IN) {
+            const bool in = op->kind == SAR_STAGE_IN;
+            const void* tsrc = in ? P.user_in : (const void*)P.comm.buf[P.rank];
+            void* tdst = in ? (void*)P.comm.buf[P.rank] : P.user_out;
+            for (uint32_t i = 0; i < d.tail_elems; ++i)
+              store_from_float(tdst, d.tail_elem0 + i, in ? P.dtype : P.user_dtype, load_as_float(tsrc, d.tail_elem0 + i, in ? P.user_dtype : P.dtype));
+            __threadfence_system();
+          } else if (d.tail_elems) { scalar_elems<T>(P, op, d.tail_elem0, d.tail_elems); __threadfence_system(); }
           // hand the item to the signal thread; wait (bounded) if its ring is full
           if (pend_tail - ld_acquire_cta(&S.pend_head) >= (uint32_t)kPendRing) {
             bulk_wait_all<0>();

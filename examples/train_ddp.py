@@ -168,8 +168,10 @@ def main() -> int:
     if args.backend == "stragglar" and args.auto_straggler:
         monitor = sp.StragglerMonitor(window=5, threshold=0.8, device=dev)
     tokens_per_step = world * args.micro_batch * seq_len
-    times = []
+    times, exposed = [], []
+    nvtx_push("Epoch 0")                                   # the ranges of the reference's loop (dp.py:157,162,286,293)
     for step in range(args.warmup + args.steps):
+        nvtx_push(f"Step {step}")
         if batches is not None:
             batch = next(batches)
             ids_host, labels_host = batch["input_ids"], batch["labels"]
@@ -178,7 +180,7 @@ def main() -> int:
             labels_host = ids_host
         if cuda:
             ids_host, labels_host = ids_host.pin_memory(), labels_host.pin_memory()
-        ev = [Stamp() for _ in range(4)]
+        ev = [Stamp() for _ in range(5)]
         dist.barrier()
         sync()
         ev[0].record()
@@ -196,33 +198,42 @@ def main() -> int:
         nvtx_push("Backward+AllReduce_Gradients")
         loss.backward()                                    # with DDP the bucket AllReduces overlap this
         nvtx_pop()
+        ev[4].record()
         if args.grad_sync != "ddp":
             nvtx_push("AllReduce_Gradients")
-            flat_sync() if flat_sync is not None else allreduce_gradients_per_param(model)
+            flat_sync() if flat_sync is not None else allreduce_gradients_per_param(model, nvtx=True)
             nvtx_pop()
         ev[2].record()
         opt.step(); sched.step(); opt.zero_grad(set_to_none=False)
         ev[3].record()
         loss_val = loss.item()                             # device -> host read of the step's result
         sync()
+        nvtx_pop()                                         # Step
         iter_ms = ev[0].ms_until(ev[3])
-        fwd, bwd = ev[0].ms_until(ev[1]), ev[1].ms_until(ev[2])
-        # the gradient AllReduces overlap the backward pass, so "AR Time" is the backward time
-        print(format_step(rank, step, fwd, bwd, loss_val, iter_ms, bwd, grad_bytes) + "\n", flush=True)
-        t = torch.tensor([iter_ms], device=dev)
+        fwd, bwd = ev[0].ms_until(ev[1]), ev[1].ms_until(ev[4])
+        # flat / per-param: the AllReduce follows the backward pass and is timed on its own (exposed communication);
+        # ddp: the bucket AllReduces overlap the backward pass, so "AR Time" is the backward time
+        ar = ev[4].ms_until(ev[2]) if args.grad_sync != "ddp" else bwd
+        print(format_step(rank, step, fwd, bwd, loss_val, iter_ms, ar, grad_bytes) + "\n", flush=True)
+        t = torch.tensor([iter_ms, ar], device=dev)
         allt = [torch.zeros_like(t) for _ in range(world)]
         dist.all_gather(allt, t)
         if monitor is not None:
             monitor.step()
         if step >= args.warmup:
-            times.append(max(float(a.item()) for a in allt))
+            times.append(max(float(a[0].item()) for a in allt))
+            exposed.append(max(float(a[1].item()) for a in allt))
+    nvtx_pop()                                             # Epoch
     if args.backend == "stragglar":
         st = sp.check_status(dev)
         assert st == 0, f"device status {st}"
     if rank == 0 and times:
         ms = sum(times) / len(times)
-        print(f"RESULT backend={args.backend} alg={args.alg} world={world} step_ms={ms:.2f} "
-              f"tokens_per_s={tokens_per_step / (ms / 1e3):.0f} delay_ms={args.delay_ms} straggler={straggler}", flush=True)
+        ar_ms = sum(exposed) / len(exposed)
+        what = "exposed_allreduce_ms" if args.grad_sync != "ddp" else "backward_with_overlapped_allreduce_ms"
+        print(f"RESULT backend={args.backend} alg={args.alg} grad_sync={args.grad_sync} world={world} step_ms={ms:.2f} "
+              f"tokens_per_s={tokens_per_step / (ms / 1e3):.0f} {what}={ar_ms:.2f} steps={len(times)} "
+              f"delay_ms={args.delay_ms} straggler={straggler}", flush=True)
     dist.destroy_process_group()
     return 0
 

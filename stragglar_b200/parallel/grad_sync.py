@@ -57,15 +57,21 @@ class FlatGradSync:
             off += g.numel()
 
 
-def allreduce_gradients_per_param(model, group=None) -> int:
-    """One AllReduce per parameter; returns the bytes reduced."""
+def allreduce_gradients_per_param(model, group=None, nvtx: bool = False) -> int:
+    """One AllReduce per parameter; returns the bytes reduced.  ``nvtx``: an ``allreduce:<parameter name>`` range
+    around every call, as the reference's script has (motivation/dp_llama.py:109-114)."""
     total = 0
     world = dist.get_world_size(group)
-    for g in _grads(model):
+    named = [(n, p.grad) for n, p in model.named_parameters() if p.requires_grad and p.grad is not None]
+    for name, g in named:
+        if nvtx and g.is_cuda:
+            torch.cuda.nvtx.range_push(f"allreduce:{name}")
         if dist.get_backend(group) in ("stragglar", "nccl"):
             dist.all_reduce(g, op=dist.ReduceOp.AVG, group=group)
         else:
             dist.all_reduce(g, group=group)
             g /= world
+        if nvtx and g.is_cuda:
+            torch.cuda.nvtx.range_pop()
         total += g.numel() * g.element_size()
     return total
