@@ -245,6 +245,15 @@ struct TableGeom {
   uint32_t round_prefix[SAR_GATE_ALL_DONE + 1];
 };
 
+// Staged mode: the last blocks of the rank only stage (every tile in, then every tile out as it becomes final) and
+// the others only walk the table, so that copying in, reducing and copying out overlap tile by tile instead of
+// following one another in every block.  A quarter of the blocks stage (local copies run at memory speed); with a
+// single block there is nobody to share with and the block does everything in turn (returns 0).
+__device__ __forceinline__ uint32_t staging_blocks(const SarLaunchParams& P, uint32_t nblocks) {
+  if (!P.user_in || nblocks < 2) return 0;
+  return nblocks >= 8 ? nblocks / 4 : 1u;
+}
+
 // All threads of the block; ends with a block barrier.
 __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t nblocks) {
   const uint32_t nrounds = P.num_rounds < SAR_MAX_ROUNDS ? P.num_rounds : SAR_MAX_ROUNDS;
@@ -273,7 +282,7 @@ __device__ void resolve_table(const SarLaunchParams& P, TableGeom& G, uint32_t n
     uint32_t table_lanes = 1;
     for (uint32_t o = 0; o < nops && o < SAR_MAX_OPS; ++o) if (P.ops[o].lane) table_lanes = 2;
     uint32_t lanes, lane, lb, lnb;
-    sar_lane_of_block(0, nblocks, table_lanes, P.lane1_eighths, &lanes, &lane, &lb, &lnb);
+    sar_lane_of_block(0, nblocks - staging_blocks(P, nblocks), table_lanes, P.lane1_eighths, &lanes, &lane, &lb, &lnb);
     G.lanes = lanes;
     G.num_rounds = nrounds;
     for (int k = 0; k < 2; ++k) {
@@ -311,14 +320,25 @@ struct ItemWalker {
   uint32_t ob, m, items, k, base_mod;
   uint32_t phase;         // 0: stage-in, 1: the table, 2: stage-out, 3: done
   uint32_t sk;            // next staging item of this block
+  bool stager, table_only;   // staged mode with several blocks: this block only stages / only walks the table
   __device__ void init(const SarLaunchParams* p, const TableGeom* g, uint32_t b, uint32_t nb) {
     P = p; G = g; ri = 0; base_mod = 0;
     block_all = b; nblocks_all = nb;
+    stager = false; table_only = false;
+    const uint32_t ns = staging_blocks(*p, nb);
     uint32_t lanes;
-    sar_lane_of_block(b, nb, g->lanes, p->lane1_eighths, &lanes, &lane, &block, &nblocks);
-    phase = p->user_in ? 0u : 1u;
+    if (ns && b >= nb - ns) {
+      // a staging block: its share of the staging items, no table items
+      stager = true;
+      block_all = b - (nb - ns); nblocks_all = ns;
+      lane = 0; block = 0; nblocks = 1; ri = g->num_rounds;
+    } else {
+      table_only = ns != 0;
+      sar_lane_of_block(b, nb - ns, g->lanes, p->lane1_eighths, &lanes, &lane, &block, &nblocks);
+    }
+    phase = (p->user_in && !table_only) ? 0u : 1u;
     sk = block_all;
-    load_round();
+    if (!stager) load_round();
   }
   __device__ void load_round() {
     while (ri < G->num_rounds) {
@@ -375,7 +395,7 @@ struct ItemWalker {
         ++ri;
         load_round();
       }
-      phase = P->user_out ? 2u : 3u;
+      phase = (P->user_out && !table_only) ? 2u : 3u;
       sk = block_all;
     }
     if (phase == 2) {
@@ -487,14 +507,30 @@ __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const 
       *arrived_mask |= need;
     }
   }
-  for (int q = 0; q < op->nsrc; ++q) {
-    const int src = op->src[q];
-    if ((op->src_ver[q] || staged) && !wait_word(P.comm.flags[src] + it.fidx, P.epoch_base + op->src_ver[q], w, SAR_TIMEOUT_FLAG))
-      return false;
+  // every flag the item depends on, polled together: the loads of one turn are independent, so waiting for seven
+  // peers' tiles costs one trip over the link per turn, not seven
+  const uint32_t* ptr[SAR_MAX_RANKS + 1];
+  uint32_t want[SAR_MAX_RANKS + 1];
+  int nf = 0;
+  for (int q = 0; q < op->nsrc; ++q)
+    if (op->src_ver[q] || staged) { ptr[nf] = P.comm.flags[op->src[q]] + it.fidx; want[nf] = P.epoch_base + op->src_ver[q]; ++nf; }
+  if (op->local_ver || staged) { ptr[nf] = P.comm.flags[P.rank] + it.fidx; want[nf] = P.epoch_base + op->local_ver; ++nf; }
+  if (nf == 0) return true;
+  if (nf == 1) return wait_word(ptr[0], want[0], w, SAR_TIMEOUT_FLAG);
+  uint32_t ns = 20;
+  for (uint64_t turn = 0;; ++turn) {
+    uint32_t v[SAR_MAX_RANKS + 1];
+    for (int i = 0; i < nf; ++i) v[i] = ld_relaxed_sys(ptr[i]);
+    bool all = true;
+    for (int i = 0; i < nf; ++i) all = all && sar_reached(v[i], want[i]);
+    if (all) { fence_sys(); return true; }   // acquire
+    if ((turn & 15) == 15) {
+      if (*(volatile uint32_t*)w.abort_flag) return false;
+      if (globaltimer() > w.deadline) { record_failure(w, SAR_TIMEOUT_FLAG); return false; }
+    }
+    __nanosleep(ns);
+    if (ns < 400) ns += ns >> 1;
   }
-  if ((op->local_ver || staged) && !wait_word(P.comm.flags[P.rank] + it.fidx, P.epoch_base + op->local_ver, w, SAR_TIMEOUT_FLAG))
-    return false;
-  return true;
 }
 
 // Announces a finished tile.  The caller has ordered the tile's stores before

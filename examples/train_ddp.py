@@ -82,6 +82,9 @@ def main() -> int:
 
     if args.backend == "stragglar":
         import stragglar_b200.parallel as sp
+        if args.grad_sync == "flat" and not args.tiny and cuda:
+            # the flat gradient buffer (2.4 GB of bf16 for the 1B shape, twice that in fp32) lives in the symmetric heap
+            os.environ.setdefault("STRAGGLAR_ARENA_MB", "6144")
         sp.configure(alg=args.alg, straggler=straggler)
         dist.init_process_group("stragglar", rank=rank, world_size=world)
     elif cuda:

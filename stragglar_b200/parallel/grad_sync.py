@@ -33,7 +33,11 @@ class FlatGradSync:
         self.buffer: Optional[torch.Tensor] = None
         if symmetric and dist.get_backend(group) == "stragglar":
             from . import empty_symmetric
-            self.buffer = empty_symmetric(self.numel, dtype=first.dtype, device=first.device, group=group)
+            try:
+                self.buffer = empty_symmetric(self.numel, dtype=first.dtype, device=first.device, group=group)
+            except RuntimeError as e:   # heap too small (STRAGGLAR_ARENA_MB): an ordinary tensor is staged instead
+                import warnings
+                warnings.warn(f"flat gradient buffer not placed in the symmetric heap: {e}")
         if self.buffer is None:
             self.buffer = torch.empty(self.numel, dtype=first.dtype, device=first.device)
 
