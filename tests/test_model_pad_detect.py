@@ -180,40 +180,6 @@ def test_cpu_affinity_from_a_fake_nvml(monkeypatch):
         os.sched_setaffinity(0, mine)
 
 
-def test_tile_level_model_of_the_executor(monkeypatch):
-    """exec_model: two ranks run near the link rate; free-running rounds of the synthesized schedule lose to rounds
-    run one after the other (the reason for round gating); the per-rank and per-round outputs are consistent."""
-    from stragglar_b200 import compiler as sc
-    from stragglar_b200.exec_model import ModelParams, simulate
-    monkeypatch.delenv("STRAGGLAR_GATE", raising=False)
-    nbytes = 96 << 20
-    coarse = ModelParams(dt_us=0.5)          # half the steps of the default
-    two = simulate(sc.compile_program("stragglar", 2, prephase=False), nbytes, blocks=32, params=coarse)
-    link_us = nbytes / (770.0 * 1e3)
-    assert 0.85 < link_us / two.time_us <= 1.0
-    prog = sc.compile_program("stragglar", 8, prephase=False)
-    free = simulate(prog, nbytes, blocks=32, timeline_us=50.0, params=coarse)
-    gated = simulate(prog, nbytes, blocks=32, round_lag=0, params=coarse)
-    floor = prog.link_bytes(nbytes) / (770.0 * 1e3)
-    assert floor < gated.time_us < free.time_us
-    assert free.items == gated.items and len(free.per_rank_us) == 8
-    assert list(free.round_span_us) == sorted(free.round_span_us) and len(free.round_span_us) == 9
-    spans = list(gated.round_span_us.values())
-    assert all(a[1] <= b[0] + 1e-9 for a, b in zip(spans, spans[1:]))        # gated rounds do not overlap
-    assert free.timeline["out"].shape[1] == 8 and float(free.timeline["out"].max()) <= 1.0 + 1e-6
-    assert max(free.port_busy["out"]) <= 1.0 + 1e-6
-    # a table compiled with gating is modelled with gating; dynamic dispatch and other constants run
-    monkeypatch.setenv("STRAGGLAR_GATE", "1")
-    auto = simulate(sc.compile_program("stragglar", 8, prephase=False), nbytes, blocks=32, params=coarse)
-    assert abs(auto.time_us - gated.time_us) < 1e-6
-    monkeypatch.delenv("STRAGGLAR_GATE")
-    dyn = simulate(prog, nbytes, blocks=32, dispatch="dynamic", window=4, params=ModelParams(flag_us=1.0, block_gbs=128.0, dt_us=0.5))
-    assert dyn.time_us > floor
-    # a straggler that is later than the pre-phase takes: what remains after its arrival is what DELAY -1 times
-    late = simulate(sc.compile_program("stragglar", 8), nbytes, blocks=32, delay_us=[0.0] * 7 + [1500.0], params=coarse)
-    assert abs((late.time_us - 1500.0) - free.time_us) < 0.02 * free.time_us
-
-
 def test_simulate_table_with_the_switched_algorithms(capsys):
     from stragglar_b200 import simulate
     assert simulate.main(["--b200", "--table"]) == 0
@@ -227,12 +193,3 @@ def test_simulate_table_with_the_switched_algorithms(capsys):
     assert a2a[0] == a2a[1] and rsag[0] < rsag[1]
 
 
-def test_exec_model_cli_compares_all_algorithms(capsys):
-    from stragglar_b200 import exec_model
-    assert exec_model.main(["all", "4", "--bytes", str(8 << 20), "--no-prephase", "--blocks", "8"]) == 0
-    out = capsys.readouterr().out.strip().splitlines()
-    names = [l.split()[0] for l in out[2:]]
-    assert names == ["stragglar", "stragglar_a2a", "ring", "rhd", "rsag", "direct"]
-    assert exec_model.main(["stragglar", "4", "--bytes", str(8 << 20), "--blocks", "8", "--rounds", "--delay-ms", "1"]) == 0
-    text = capsys.readouterr().out
-    assert "straggler held back 1 ms" in text and "round  0:" in text
