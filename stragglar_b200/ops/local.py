@@ -174,6 +174,15 @@ class LocalComm:
                        store_window, uin, uin, udt)
         ptrs = (C.c_void_p * self.n)(*[t.data_ptr() for t in tensors])
         dl = (C.c_uint64 * self.n)(*[int(d * 1e6) for d in delay_ms]) if delay_ms is not None else None
+        # The ranks run on streams of the communicator: make them wait for what the caller has queued on the
+        # current torch stream of every device involved (fills, clones, reference sums), so that the collective
+        # neither reads inputs that are not written yet nor overwrites tensors that are still being read.
+        import torch
+        for r in range(self.n):
+            dev = tensors[r].device
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(dev))
+            torch.cuda.ExternalStream(cuda_lib().sar_local_stream(self._h, r), device=dev).wait_event(ev)
         err = C.create_string_buffer(256)
         rc = cuda_lib().sar_local_run(self._h, program._h, ptrs, t0.numel(), _dtype_code(t0), C.byref(opts), dl, err, 256)
         if rc:

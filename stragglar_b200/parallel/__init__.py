@@ -90,7 +90,12 @@ def algorithm_for(nbytes: int, device="cuda", group=None) -> str:
 
 def empty_symmetric(numel: int, dtype=None, device="cuda", group=None):
     """A 1-D tensor in the backend's symmetric heap.  Collective: every rank
-    must call it with the same sizes in the same order."""
+    must call it with the same sizes in the same order.
+
+    Collectives on such a tensor (or on equal slices of it) run in place: peers read and write the tensor itself.
+    Every rank of a collective must then pass its tensor of the same allocation at the same offset; a rank that
+    passes an ordinary tensor instead takes the staged path while its peers reach into its heap, and the result
+    is wrong (or the collective times out).  The same holds the other way round."""
     import torch
     dev = torch.device(device)
     if dev.type == "cuda" and dev.index is None:
@@ -101,7 +106,9 @@ def empty_symmetric(numel: int, dtype=None, device="cuda", group=None):
 
 
 def all_reduce_ex(tensor, average: bool = False, comm_dtype=None, group=None):
-    """AllReduce with the cast to ``comm_dtype`` fused into staging; returns a Work."""
+    """AllReduce with an explicit dtype on the wire; returns a Work.  For an ordinary CUDA tensor the casts to and
+    from ``comm_dtype`` (and the division by world_size of ``average``) happen inside the one kernel that also copies
+    the tensor into the peer-reachable staging area and back."""
     return _ext().allreduce_ex(backend_of(tensor.device, group), tensor, average, comm_dtype)
 
 
