@@ -122,11 +122,13 @@ ProcessGroupStragglar::~ProcessGroupStragglar() {
   }
 }
 
-// "auto" picks per call: with a declared straggler the NVSwitch-native straggler-aware variant
-// (every rank moves exactly S bytes per direction and the pre-phase hides in the straggler's
-// delay); with none, the one-shot reduce-scatter + all-gather up to 512 MiB and the ring above,
-// which is where the two cross on an 8-GPU NVSwitch box.  The choice depends only on what every
-// rank knows (message size, declared straggler), so all ranks make the same one.
+// "auto" picks per call, from what every rank knows (message size, declared straggler), so all ranks agree.
+// With a declared straggler: stragglar_a2a, whose pre-phase hides in the straggler's delay and whose ranks then
+// move exactly S bytes per direction (8 x B200, net of a 5 ms delay: 25 MiB 0.145 ms, 100 MiB 0.274, 1 GiB 1.79,
+// against 0.137 / 0.319 / 2.58 for NCCL and 2.21 for the faithful schedule at 1 GiB).  With nobody declared late the
+// pre-phase would be on the critical path (1 GiB: 4.66 ms), so the one-shot reduce-scatter + all-gather serves up to
+// 512 MiB (1 / 4 / 25 / 100 MiB: 0.068 / 0.075 / 0.134 / 0.326 ms on symmetric tensors) and the ring above, where
+// the two are level (2.86 / 2.85 ms at 1 GiB).
 std::string ProcessGroupStragglar::algorithm_for(size_t bytes) const {
   if (opts_.alg != "auto") return opts_.alg;
   const int n = getSize();
