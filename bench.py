@@ -154,8 +154,8 @@ def run_reference(args) -> int:
         nbytes = bench_bytes(args.bytes, n)
         with ClockSampler(0) as cs:
             t0 = time.time()
-            # the program discards its iteration 0 (stragglar/allreduce_8GPU.cu:1053): one more, so that `steps` are timed
-            p = subprocess.run([exe, str(nbytes), args.alg, str(args.steps + 1), str(args.delay_ms)], capture_output=True,
+            # the program runs one iteration more than asked and discards the first (stragglar/allreduce_8GPU.cu:1009,1053)
+            p = subprocess.run([exe, str(nbytes), args.alg, str(args.steps), str(args.delay_ms)], capture_output=True,
                                text=True, timeout=1800)
             wall = time.time() - t0
         rows = [l.split(",") for l in p.stdout.splitlines() if l.startswith(args.alg + ",")]
@@ -177,7 +177,7 @@ def run_reference(args) -> int:
                     "e2e": e2e,
                     "config": bench_config(args.alg, n, nbytes, args.delay_ms, n - 1),
                     "notes": {"timing": "device 0 events only (the reference's own clock), nominal delay subtracted",
-                              "warmup": "the program's own: 10 send/recv exchanges and a discarded first iteration, "
+                              "warmup": "the program's own: 10 send/recv exchanges and one discarded extra iteration, "
                                         "whatever --warmup says (stragglar/allreduce_8GPU.cu:992-1006,1053)",
                               "processes": f"1 process x {n} GPUs, NCCL send/recv"}})
         print(json.dumps(out), flush=True)
