@@ -549,6 +549,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupStragglar::reduce(std::vector<at::Ten
   at::Tensor& x = tensors[0];
   const size_t es = x.element_size();
   uint64_t piece = t.staging_bytes() / es / 256 * 256;
+  TORCH_CHECK(piece > 0, "staging area too small");
   char* stage = t.data(getRank()) + t.staging_off();
   const float scale = scale_for(opts.reduceOp, getSize());
   for (uint64_t off = 0; off < (uint64_t)x.numel(); off += piece) {
