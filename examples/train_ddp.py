@@ -58,6 +58,10 @@ def main() -> int:
                     help="ddp: DistributedDataParallel buckets overlapped with backward; flat: one all_reduce of "
                          "the flattened gradients after backward (the reference's dp.py); per-param: one all_reduce "
                          "per parameter (the reference's dp_llama.py)")
+    ap.add_argument("--hook", default="fused", choices=["fused", "symmetric", "bf16"],
+                    help="stragglar backend, ddp: fused = all_reduce of the bucket with the fused average (one staged "
+                         "kernel per bucket); symmetric = buckets reduced in buffers of the symmetric heap; bf16 = fused, "
+                         "bfloat16 on the wire")
     ap.add_argument("--auto-straggler", action="store_true",
                     help="find the late rank at run time (StragglerMonitor) instead of trusting --straggler")
     ap.add_argument("--model-dir", default=None, help="checkpoint directory (config.json + safetensors)")
@@ -82,7 +86,7 @@ def main() -> int:
 
     if args.backend == "stragglar":
         import stragglar_b200.parallel as sp
-        if args.grad_sync == "flat" and not args.tiny and cuda:
+        if (args.grad_sync == "flat" or args.hook == "symmetric") and not args.tiny and cuda:
             # the flat gradient buffer (2.4 GB of bf16 for the 1B shape, twice that in fp32) lives in the symmetric heap
             os.environ.setdefault("STRAGGLAR_ARENA_MB", "6144")
         sp.configure(alg=args.alg, straggler=straggler)
@@ -131,7 +135,8 @@ def main() -> int:
     if args.grad_sync == "ddp":
         ddp = DDP(model, device_ids=[local] if cuda else None, bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
         if args.backend == "stragglar":
-            ddp.register_comm_hook(None, sp.fused_avg_hook)
+            ddp.register_comm_hook(None, {"fused": sp.fused_avg_hook, "bf16": sp.bf16_fused_avg_hook}.get(args.hook)
+                                   or sp.SymmetricBucketHook())
     else:
         ddp = model                       # gradients are averaged by hand after the backward pass
         for p in model.parameters():

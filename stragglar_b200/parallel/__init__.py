@@ -195,6 +195,42 @@ def fused_avg_hook(state, bucket):
     return fut.then(lambda f: f.value()[0])
 
 
+class SymmetricBucketHook:
+    """DDP communication hook that reduces every gradient bucket in a buffer of the symmetric heap.
+
+    DistributedDataParallel allocates its buckets itself, outside the heap that peers can reach, so a bucket handed
+    to ``dist.all_reduce`` takes the staged path.  This hook keeps one symmetric buffer per bucket (allocated on the
+    bucket's first use; a collective allocation, made in bucket order, which is the same on every rank), copies the
+    bucket in, reduces in place with the fused average, and copies the result back: two local copies at memory speed
+    around the fastest collective path.  The symmetric heap must hold all buckets (STRAGGLAR_ARENA_MB).
+
+        ddp.register_comm_hook(None, sp.SymmetricBucketHook())
+    """
+
+    def __init__(self, group=None):
+        self.group = group
+        self._bufs = {}
+        self.__name__ = self.__qualname__ = "symmetric_bucket_hook"   # DDP logs the hook's name
+
+    def __call__(self, state, bucket):
+        import torch.distributed as dist
+        group = self.group if self.group is not None else (state if state is not None else dist.group.WORLD)
+        buf = bucket.buffer()
+        key = bucket.index()
+        sym = self._bufs.get(key)
+        if sym is None or sym.numel() != buf.numel() or sym.dtype != buf.dtype:
+            # DDP rebuilds its buckets once after the first iteration: sizes change, on every rank alike
+            sym = empty_symmetric(buf.numel(), dtype=buf.dtype, device=buf.device, group=group)
+            self._bufs[key] = sym
+        sym.copy_(buf)
+        fut = dist.all_reduce(sym, op=dist.ReduceOp.AVG, group=group, async_op=True).get_future()
+
+        def back(f):
+            buf.copy_(sym)
+            return buf
+        return fut.then(back)
+
+
 def bf16_fused_avg_hook(state, bucket):
     """DDP communication hook: gradients travel as bfloat16.  One kernel per bucket reads the fp32 bucket tile by
     tile, converts it to bfloat16 into the buffer the peers reach, reduces (fp32 accumulation, the division by

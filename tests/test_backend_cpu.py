@@ -154,7 +154,7 @@ def test_collectives(world):
     run_ranks(world, _collectives)
 
 
-def _ddp(rank, world):
+def _ddp(rank, world, hook="fused"):
     import stragglar_b200.parallel as sp
     from torch.nn.parallel import DistributedDataParallel as DDP
     torch.manual_seed(0)
@@ -162,11 +162,13 @@ def _ddp(rank, world):
     ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
     ref.load_state_dict(model.state_dict())
     ddp = DDP(model, bucket_cap_mb=0.001)
-    ddp.register_comm_hook(None, sp.fused_avg_hook)
+    ddp.register_comm_hook(None, sp.fused_avg_hook if hook == "fused" else sp.SymmetricBucketHook())
     xs = [torch.randn(8, 16, generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
     ys = [torch.randn(8, 4, generator=torch.Generator().manual_seed(200 + r)) for r in range(world)]
-    loss = torch.nn.functional.mse_loss(ddp(xs[rank]), ys[rank])
-    loss.backward()
+    for _ in range(3 if hook != "fused" else 1):   # several steps: DDP rebuilds its buckets after the first
+        ddp.zero_grad()
+        loss = torch.nn.functional.mse_loss(ddp(xs[rank]), ys[rank])
+        loss.backward()
     # reference: average of the per-rank gradients computed locally
     total = None
     for r in range(world):
@@ -180,6 +182,10 @@ def _ddp(rank, world):
 
 def test_distributed_data_parallel_on_the_backend():
     run_ranks(2, _ddp)
+
+
+def test_ddp_with_buckets_reduced_in_the_symmetric_heap():
+    run_ranks(2, _ddp, "symmetric")
 
 
 def _late_rank_times_out(rank, world):
