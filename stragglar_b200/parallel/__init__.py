@@ -112,6 +112,49 @@ def all_reduce_ex(tensor, average: bool = False, comm_dtype=None, group=None):
     return _ext().allreduce_ex(backend_of(tensor.device, group), tensor, average, comm_dtype)
 
 
+class HostStreamedAllReduce:
+    """AllReduce of data that arrives from pinned host memory every step, with the host-to-device copy streamed
+    through the collective: the tensor is cut into ``pieces``; piece k is reduced (in place, in a tensor of the
+    symmetric heap) as soon as it has landed on the device while piece k+1 is still being copied on a stream of
+    its own, so the collective -- and whatever holds the ranks back before it, e.g. a late rank -- hides behind
+    the copy instead of following it.
+
+        stream = sp.HostStreamedAllReduce(numel, dtype=torch.float32, device="cuda")   # collective: allocates
+        out = stream(host_tensor, op=dist.ReduceOp.AVG)      # the device tensor that holds the result
+
+    Everything is enqueued asynchronously; the caller's current stream is ordered after the last piece.
+    """
+
+    def __init__(self, numel: int, dtype=None, device="cuda", pieces: int = 8, group=None):
+        import torch
+        self.group = group
+        self.out = empty_symmetric(numel, dtype=dtype, device=device, group=group)
+        n = max(1, min(pieces, numel // 4096 or 1))
+        step = -(-numel // n)
+        step = -(-step // 64) * 64                      # pieces start on 256-byte boundaries
+        self.bounds = [(b, min(b + step, numel)) for b in range(0, numel, step)]
+        self.copy_stream = torch.cuda.Stream(self.out.device)
+        self.events = [torch.cuda.Event() for _ in self.bounds]
+
+    def __call__(self, host_tensor, op=None, before_collective=None):
+        """``before_collective``: called once on the current stream before the first piece is reduced (a hook for
+        whatever precedes the collective on this rank); the copies do not wait for it."""
+        import torch
+        import torch.distributed as dist
+        op = dist.ReduceOp.SUM if op is None else op
+        cur = torch.cuda.current_stream(self.out.device)
+        self.copy_stream.wait_stream(cur)                # the previous result has been consumed
+        if before_collective is not None:
+            before_collective()
+        for (b, e), ev in zip(self.bounds, self.events):
+            with torch.cuda.stream(self.copy_stream):
+                self.out[b:e].copy_(host_tensor[b:e], non_blocking=True)
+                ev.record(self.copy_stream)
+            cur.wait_event(ev)
+            dist.all_reduce(self.out[b:e], op=op, group=self.group)
+        return self.out
+
+
 def check_status(device="cuda", group=None) -> int:
     """Wait for the communication stream and return the device status word
     (0 = ok; see ``stragglar_b200.compiler.status_string``)."""

@@ -219,3 +219,24 @@ def test_late_rank_raises_through_the_work_object():
         run_ranks(2, _late_rank_cuda)
     finally:
         del os.environ["STRAGGLAR_TIMEOUT_MS"]
+
+
+def _host_streamed(rank, world):
+    """sp.HostStreamedAllReduce: pieces of a pinned host tensor are reduced as they land on the device."""
+    import stragglar_b200.parallel as sp
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    n = 3_000_017
+    host = _seeded(rank, n).pin_memory()
+    want = torch.stack([_seeded(r, n).double() for r in range(world)]).sum(0) / world
+    stream = sp.HostStreamedAllReduce(n, dtype=torch.float32, device=dev, pieces=5)
+    for _ in range(2):
+        out = stream(host, op=dist.ReduceOp.AVG)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(out.double().cpu(), want, atol=2e-5, rtol=1e-6)
+    assert sp.check_status(dev) == 0
+
+
+@pytest.mark.multigpu
+def test_host_streamed_allreduce():
+    run_ranks(2, _host_streamed)
