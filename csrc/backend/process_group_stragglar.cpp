@@ -325,8 +325,9 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
     if (t.cuda() && opts_.blocks <= 0 && c.blocks_hint > 0 && c.blocks_hint < blocks) blocks = c.blocks_hint;
     if (t.cuda() && opts_.blocks <= 0 && n == 1 && blocks == 128) blocks = 148;   // a lone rank: one block per SM
     const bool gated = c.gate_rounds && count * esize >= sar::gate_min_bytes();
+    // staged launches poll a flag over the link for every tile they read from a peer, version 0 included: larger tiles
     const uint32_t tile_max = opts_.tile_bytes ? opts_.tile_bytes
-                            : (t.cuda() ? (gated ? sar::gate_tile_bytes() : sar_cuda_default_tile_bytes(opts_.path)) : (128u << 10));
+                            : (t.cuda() ? ((gated || user) ? sar::gate_tile_bytes() : sar_cuda_default_tile_bytes(opts_.path)) : (128u << 10));
     const uint32_t tile_elems = sar::pick_tile_elems(count, esize, (uint32_t)c.num_chunks, (uint32_t)blocks, 2048, tile_max);
     const SarGeom g = sar::make_geom(count, esize, (uint32_t)c.num_chunks, tile_elems);
     TORCH_CHECK((uint64_t)g.tiles_per_chunk * g.num_chunks <= SAR_FLAG_CAPACITY, "tensor too large for the flag array");
@@ -367,7 +368,14 @@ void ProcessGroupStragglar::run_program(Side& s, const sar::Program& prog, size_
       P.gate_base = epoch64; P.gate_slack = sar::gate_slack(g.tiles_per_chunk);
       P.stages = (uint32_t)c.stages_hint;
       P.lane1_eighths = (uint32_t)c.lane1_eighths;
-      SAR_CUDA_CHECK(sar_cuda_launch(&P, opts_.path, blocks, opts_.threads, s.stream->stream()));
+      int launch_blocks = blocks;
+      if (user) {
+        // staging blocks on top of the table's: local copies need many blocks to run at memory speed
+        const int extra = std::max(1, std::min(64, 144 - blocks));
+        P.staging_blocks = (uint32_t)extra;
+        launch_blocks = blocks + extra;
+      }
+      SAR_CUDA_CHECK(sar_cuda_launch(&P, opts_.path, launch_blocks, opts_.threads, s.stream->stream()));
       ++launches_;
     } else {
       sar::HostRankView v;

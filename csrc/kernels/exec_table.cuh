@@ -247,10 +247,13 @@ struct TableGeom {
 
 // Staged mode: the last blocks of the rank only stage (every tile in, then every tile out as it becomes final) and
 // the others only walk the table, so that copying in, reducing and copying out overlap tile by tile instead of
-// following one another in every block.  A quarter of the blocks stage (local copies run at memory speed); with a
-// single block there is nobody to share with and the block does everything in turn (returns 0).
+// following one another in every block.  The launch says how many blocks stage (a block moves about 30 GB/s through
+// its ring whatever the distance, so local copies at memory speed take many blocks: the backend adds up to 64 to
+// the blocks that walk the table); by default a quarter of the blocks.  With a single block there is nobody to
+// share with and the block does everything in turn (returns 0).
 __device__ __forceinline__ uint32_t staging_blocks(const SarLaunchParams& P, uint32_t nblocks) {
   if (!P.user_in || nblocks < 2) return 0;
+  if (P.staging_blocks) return P.staging_blocks < nblocks ? P.staging_blocks : nblocks - 1;
   return nblocks >= 8 ? nblocks / 4 : 1u;
 }
 
@@ -512,8 +515,13 @@ __device__ bool wait_item_ready(const SarLaunchParams& P, const Item& it, const 
   const uint32_t* ptr[SAR_MAX_RANKS + 1];
   uint32_t want[SAR_MAX_RANKS + 1];
   int nf = 0;
+  // (A push names the version it replaces in the destination.  Version 0 there, in staged mode, is the
+  // destination's own copy-in of that tile, and whatever is pushed into a slot contains that rank's contribution to
+  // the chunk or follows a read of it, both of which waited for that copy-in: the push is ordered after it already.)
   for (int q = 0; q < op->nsrc; ++q)
-    if (op->src_ver[q] || staged) { ptr[nf] = P.comm.flags[op->src[q]] + it.fidx; want[nf] = P.epoch_base + op->src_ver[q]; ++nf; }
+    if (op->src_ver[q] || (staged && op->kind != SAR_PUSH)) {
+      ptr[nf] = P.comm.flags[op->src[q]] + it.fidx; want[nf] = P.epoch_base + op->src_ver[q]; ++nf;
+    }
   if (op->local_ver || staged) { ptr[nf] = P.comm.flags[P.rank] + it.fidx; want[nf] = P.epoch_base + op->local_ver; ++nf; }
   if (nf == 0) return true;
   if (nf == 1) return wait_word(ptr[0], want[0], w, SAR_TIMEOUT_FLAG);

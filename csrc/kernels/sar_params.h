@@ -52,7 +52,7 @@ struct SarLaunchParams {
   void* user_out;
   int32_t user_dtype;     // SarDtype of user_in / user_out
   uint8_t final_ver[SAR_MAX_CHUNKS];   // version of this rank's slot of every chunk when the table is done
-  uint32_t pad2;
+  uint32_t staging_blocks; // blocks of the launch (the last ones) that only stage; 0: a quarter of the blocks
   uint64_t delay_ns;      // spin this long before arriving (a late rank when ranks share one launch)
   SarMcGroup mc[2];       // multicast views (simt path): all ranks, and e.g. the non-stragglers
 };
