@@ -97,7 +97,7 @@ def test_backend_on_all_gpus():
     run_ranks(world, _cuda_collectives)
 
 
-def _ddp_cuda(rank, world):
+def _ddp_cuda(rank, world, hook="fused"):
     import stragglar_b200.parallel as sp
     from torch.nn.parallel import DistributedDataParallel as DDP
     torch.cuda.set_device(rank)
@@ -107,7 +107,8 @@ def _ddp_cuda(rank, world):
     ref = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.GELU(), torch.nn.Linear(256, 8)).to(dev)
     ref.load_state_dict(model.state_dict())
     ddp = DDP(model, device_ids=[rank], bucket_cap_mb=0.01)
-    ddp.register_comm_hook(None, sp.fused_avg_hook)
+    hooks = {"fused": sp.fused_avg_hook, "bf16": sp.bf16_fused_avg_hook}
+    ddp.register_comm_hook(None, hooks.get(hook) or sp.SymmetricBucketHook())
     xs = [torch.randn(16, 64, generator=torch.Generator().manual_seed(100 + r)).to(dev) for r in range(world)]
     ys = [torch.randn(16, 8, generator=torch.Generator().manual_seed(200 + r)).to(dev) for r in range(world)]
     for _ in range(2):
@@ -119,14 +120,16 @@ def _ddp_cuda(rank, world):
         torch.nn.functional.mse_loss(ref(xs[r]), ys[r]).backward()
         g = [p.grad.clone() for p in ref.parameters()]
         total = g if total is None else [a + b for a, b in zip(total, g)]
+    tol = dict(atol=1e-5, rtol=1e-4) if hook != "bf16" else dict(atol=2e-2, rtol=2e-2)
     for p, g in zip(model.parameters(), total):
-        torch.testing.assert_close(p.grad, g / world, atol=1e-5, rtol=1e-4)
+        torch.testing.assert_close(p.grad, g / world, **tol)
     assert sp.check_status(dev) == 0
 
 
 @pytest.mark.multigpu
-def test_ddp_with_fused_average_hook():
-    run_ranks(2, _ddp_cuda)
+@pytest.mark.parametrize("hook", ["fused", "symmetric", "bf16"])
+def test_ddp_with_fused_average_hook(hook):
+    run_ranks(2, _ddp_cuda, hook)
 
 
 @pytest.mark.multigpu
