@@ -111,6 +111,13 @@ class Table:
     """One compiled phase: a :class:`RankTable` per physical rank.  Owned by
     its :class:`Program`."""
 
+    def final_versions(self, rank: int):
+        """Per chunk, the version rank ``rank``'s slot has when the collective is done (how often the slot is
+        rewritten): what a staged launch waits for before it copies a tile back to the caller's tensor."""
+        out = (C.c_uint8 * 16)()
+        lib().sar_table_final_ver(self._h, rank, out)
+        return [int(v) for v in out[: self.num_chunks]]
+
     def __init__(self, handle: int, program: "Program"):
         L = lib()
         self._h = handle
@@ -125,6 +132,7 @@ class Table:
         self.gate_rounds = bool(L.sar_table_gate_rounds(handle))   # rounds run one after the other (STRAGGLAR_GATE)
         self.lane1_eighths = L.sar_table_lane1_eighths(handle)     # share of the blocks of lane 1 (4: half)
         self.participants = L.sar_table_participants(handle)
+        L.sar_table_final_ver.restype, L.sar_table_final_ver.argtypes = None, [C.c_void_p, C.c_int, C.POINTER(C.c_uint8)]
         self.ranks: List[RankTable] = []
         for r in range(self.n):
             k = L.sar_table_num_ops(handle, r)

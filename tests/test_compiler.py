@@ -272,3 +272,22 @@ def test_lane_split_share(monkeypatch):
         assert sc.host_allreduce(prog, bufs, blocks=5, tile_elems=128) == 0
         for b in bufs:
             np.testing.assert_allclose(b.astype(np.float64), want, atol=2e-5)
+
+
+def test_final_versions_match_the_ops():
+    """The final version of every slot (what staged launches wait for) is the newest version any op gives it."""
+    for alg, n in (("stragglar", 8), ("stragglar_a2a", 6), ("ring", 4), ("rsag", 4), ("rhd", 8)):
+        t = sc.compile_table(alg, n)
+        newest = [[0] * t.num_chunks for _ in range(n)]
+        for r in range(n):
+            for op in t.ranks[r].ops:
+                kind, chunk = int(op["kind"]), int(op["chunk"])
+                if kind != 3:                                   # everything but a push rewrites the own slot
+                    newest[r][chunk] = max(newest[r][chunk], int(op["post_ver"]))
+                if kind in (2, 3):                              # REDUCE_PUSH / PUSH rewrite the peers' slots
+                    for q in range(int(op["nsrc"])):
+                        peer = int(op["src"][q])
+                        newest[peer][chunk] = max(newest[peer][chunk], int(op["push_ver"]))
+        for r in range(n):
+            assert t.final_versions(r) == newest[r], (alg, n, r)
+            assert all(v >= 1 for v in newest[r])               # every slot ends rewritten (the sum lands everywhere)
