@@ -56,9 +56,14 @@ int main() {
   int failures = check_validation(), runs = 0;
   const char* algs[] = {"stragglar", "stragglar_a2a", "ring", "rhd", "direct", "rsag"};
   // round gating (rounds one after the other) is run for every algorithm too, on the lowerings that ship
-  for (const char* gate : {"0", "all"})
+  // gated twice: with the default slack (a round opens early, items wait for their flags) and with the full barrier
+  // (slack 0: gated items skip their flag waits, the barrier alone orders them)
+  for (const char* mode : {"0", "all", "all/barrier"})
   for (const char* copy : {"pull", "push"})
     for (const char* lanes : {"1", "2"}) {
+      const bool barrier = std::string(mode) == "all/barrier";
+      const char* gate = barrier ? "all" : mode;
+      if (barrier) setenv("STRAGGLAR_GATE_SLACK", "0", 1); else unsetenv("STRAGGLAR_GATE_SLACK");
       if (std::string(gate) == "all" && std::string(copy) == "push" && std::string(lanes) == "2") continue;   // keeps the run short
       setenv("STRAGGLAR_GATE", gate, 1);
       setenv("STRAGGLAR_COPY", copy, 1);
@@ -88,11 +93,11 @@ int main() {
             delay[straggler < 0 ? n - 1 : straggler] = 2.0;   // the straggler is 2 ms late
             const uint32_t st = sar::host_execute_program(prog, ptrs.data(), count, SAR_F32, 32, 0.5f, 4, delay.data(), 20.0);
             ++runs;
-            if (st) { printf("status %u: %s n=%d copy=%s lanes=%s gate=%s\n", st, alg, n, copy, lanes, gate); ++failures; continue; }
+            if (st) { printf("status %u: %s n=%d copy=%s lanes=%s gate=%s\n", st, alg, n, copy, lanes, mode); ++failures; continue; }
             for (int r = 0; r < n; ++r)
               for (uint64_t i = 0; i < count; ++i)
                 if (std::fabs(buf[r][i] - 0.5 * want[i]) > 1e-5) {
-                  printf("wrong value: %s n=%d copy=%s lanes=%s gate=%s rank %d elem %llu\n", alg, n, copy, lanes, gate, r, (unsigned long long)i);
+                  printf("wrong value: %s n=%d copy=%s lanes=%s gate=%s rank %d elem %llu\n", alg, n, copy, lanes, mode, r, (unsigned long long)i);
                   ++failures;
                   r = n;
                   break;
