@@ -111,6 +111,7 @@ ProcessGroupStragglar::ProcessGroupStragglar(const c10::intrusive_ptr<c10d::Stor
   if (const char* b = getenv("STRAGGLAR_THREADS")) if (*b) opts_.threads = atoi(b);
   if (const char* b = getenv("STRAGGLAR_TILE_BYTES")) if (*b) opts_.tile_bytes = (uint32_t)atoi(b);
   if (const char* b = getenv("STRAGGLAR_TIMEOUT_MS")) if (*b) opts_.timeout_s = atof(b) / 1e3;
+  if (const char* b = getenv("STRAGGLAR_CHECK_ARGS")) if (*b) opts_.check_args = atoi(b) != 0;
   (void)program();   // fail early on a bad algorithm / rank count
 }
 
@@ -427,6 +428,29 @@ std::pair<int64_t, int64_t> ProcessGroupStragglar::last_trace() {
   return {(int64_t)v[0], (int64_t)v[1]};
 }
 
+// The in-place path hands the kernel this rank's heap offset for every peer, and the staged path waits for tile
+// flags where the in-place path waits for arrival words: ranks that pass different kinds of tensors (or different
+// sizes) to one collective compute garbage or time out.  With check_args every rank publishes what it was given and
+// compares it with everybody else's before anything is launched.
+void ProcessGroupStragglar::check_same_arguments(uint64_t count, int tensor_dtype, int comm_dtype, int64_t heap_off) {
+  const int n = getSize(), me = getRank();
+  if (n == 1) return;
+  const uint64_t seq = check_seq_++;
+  const std::string mine = std::to_string(count) + "/" + std::to_string(tensor_dtype) + "/" + std::to_string(comm_dtype) +
+                           "/" + (heap_off >= 0 ? "symmetric@" + std::to_string(heap_off) : std::string("ordinary"));
+  const std::string base = prefix_ + "/chk/" + std::to_string(seq) + "/";
+  store_->set(base + std::to_string(me), std::vector<uint8_t>(mine.begin(), mine.end()));
+  for (int r = 0; r < n; ++r) {
+    if (r == me) continue;
+    auto v = store_->get(base + std::to_string(r));
+    const std::string theirs(v.begin(), v.end());
+    TORCH_CHECK(theirs == mine, "stragglar backend: ranks passed different arguments to one AllReduce (count/tensor dtype/"
+                "wire dtype/placement): rank ", me, " has ", mine, ", rank ", r, " has ", theirs,
+                ". Every rank must pass a tensor of the same size and kind (the same symmetric allocation at the same "
+                "offset, or an ordinary tensor everywhere).");
+  }
+}
+
 // ------------------------------------------------------------------- allreduce
 void ProcessGroupStragglar::allreduce_impl(Side& s, at::Tensor& tensor, float scale, std::optional<at::ScalarType> comm_dtype) {
   Transport& t = *s.t;
@@ -440,6 +464,7 @@ void ProcessGroupStragglar::allreduce_impl(Side& s, at::Tensor& tensor, float sc
   const sar::Program& prog = program(count * csize);
   char* ptr = (char*)tensor.data_ptr();
   const int64_t hoff = (cdt == tdt) ? t.heap_offset(ptr, count * csize) : -1;
+  if (opts_.check_args) check_same_arguments(count, dtype_code(tdt), cdc, (hoff >= 0 && (((uintptr_t)ptr) & 15) == 0) ? hoff : -1);
   if (hoff >= 0 && (((uintptr_t)ptr) & 15) == 0) {
     run_program(s, prog, (size_t)hoff, count, cdt, scale);   // in place, no staging
     return;
@@ -992,6 +1017,7 @@ static c10::intrusive_ptr<c10d::Backend> create_backend(const c10::intrusive_ptr
   if (options.contains("arena_bytes")) o.arena_bytes = options["arena_bytes"].cast<size_t>();
   if (options.contains("staging_bytes")) o.staging_bytes = options["staging_bytes"].cast<size_t>();
   if (options.contains("schedule_text")) o.schedule_text = options["schedule_text"].cast<std::string>();
+  if (options.contains("check_args")) o.check_args = options["check_args"].cast<bool>();
   return c10::make_intrusive<ProcessGroupStragglar>(
       store, rank, size, std::chrono::duration_cast<std::chrono::milliseconds>(timeout), o);
 }

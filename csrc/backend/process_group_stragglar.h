@@ -50,6 +50,10 @@ struct BackendOptions {
   size_t arena_bytes = 0;          // data region per rank (0: STRAGGLAR_ARENA_MB or 1 GiB on CUDA, 64 MiB on CPU)
   size_t staging_bytes = 0;        // part of the arena used to stage foreign tensors (0: a quarter, at most 256 MiB)
   std::string schedule_text;       // overrides the built-in StragglAR schedule
+  bool check_args = false;         // STRAGGLAR_CHECK_ARGS=1: every AllReduce first compares, through the Store, what the
+                                   // ranks passed (element count, dtypes, symmetric offset or "ordinary tensor"); a
+                                   // mismatch raises on every rank instead of producing wrong sums.  A debugging aid:
+                                   // it costs a Store round trip per collective.
 };
 
 // The failure word of one device side of a process group, shared with the Work objects it hands out.
@@ -189,6 +193,8 @@ class ProcessGroupStragglar : public c10d::Backend {
   std::mutex mu_;
   int64_t launches_ = 0;
   uint64_t alloc_seq_ = 0;
+  uint64_t check_seq_ = 0;
+  void check_same_arguments(uint64_t count, int tensor_dtype, int comm_dtype, int64_t heap_off);
   std::map<std::pair<bool, int>, uint32_t> send_seq_, recv_seq_;   // (cuda?, peer) -> handshakes so far
 };
 

@@ -31,7 +31,9 @@ def configure(**options) -> None:
     """Options of process groups created afterwards: alg ('stragglar' | 'stragglar_a2a' | 'ring' | 'rhd' |
     'direct' | 'rsag' | 'auto': the straggler-aware variant while a straggler is declared, else rsag or ring by
     size), straggler (physical rank; -1: the last rank, or nobody for 'auto'), path ('tma' | 'simt' | 'simta'),
-    blocks, threads, tile_bytes, timeout_s, arena_bytes, staging_bytes, schedule_text.  Lowering switches are read
+    blocks, threads, tile_bytes, timeout_s, arena_bytes, staging_bytes, schedule_text, check_args (also
+    STRAGGLAR_CHECK_ARGS=1: every AllReduce first compares through the Store what the ranks passed -- size, dtypes,
+    symmetric offset or ordinary tensor -- and raises on a mismatch; a debugging aid, one Store round trip per call).  Lowering switches are read
     from the environment when a program is first built: STRAGGLAR_GATE, STRAGGLAR_COPY, STRAGGLAR_LANES,
     STRAGGLAR_LANE1_EIGHTHS."""
     _options.update(options)

@@ -459,3 +459,27 @@ def _ddp_unused(rank, world):
 
 def test_ddp_with_unused_parameters():
     run_ranks(2, _ddp_unused)
+
+
+def _mismatched_arguments(rank, world):
+    # STRAGGLAR_CHECK_ARGS=1: a rank that passes another kind of tensor (or another size) than its peers is told so
+    import stragglar_b200.parallel as sp
+    sym = sp.empty_symmetric(256, device="cpu")
+    sym.fill_(1.0)
+    x = sym if rank == 0 else torch.ones(256)          # rank 0: symmetric heap, rank 1: an ordinary tensor
+    with pytest.raises(RuntimeError, match="different arguments"):
+        dist.all_reduce(x)
+    y = torch.ones(128 if rank == 0 else 64)
+    with pytest.raises(RuntimeError, match="different arguments"):
+        dist.all_reduce(y)
+    z = torch.full((512,), float(rank + 1))            # the same everywhere: goes through
+    dist.all_reduce(z)
+    assert float(z[0]) == 3.0
+
+
+def test_argument_check_names_mismatched_ranks():
+    os.environ["STRAGGLAR_CHECK_ARGS"] = "1"
+    try:
+        run_ranks(2, _mismatched_arguments)
+    finally:
+        del os.environ["STRAGGLAR_CHECK_ARGS"]
