@@ -62,3 +62,24 @@ def test_both_arms_describe_the_same_configuration():
     assert bench.bench_bytes(1000, 8) == 980
     assert set(bench.bench_config("ring", 8, 64, 0.0, 7)) == {"model", "bytes_per_gpu", "delay_ms", "straggler_rank",
                                                                "global_batch", "seq_len", "parallelism", "l2"}
+
+
+def test_summarize_reads_old_and_new_csv_rows(tmp_path, capsys):
+    """bench/summarize.py: rows of the reference (6 columns), of earlier runs (14) and of the current program (15, with the
+    in-kernel time) summarise side by side; the delay is taken off the net time."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("summarize", os.path.join(ROOT, "bench", "summarize.py"))
+    sm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sm)
+    f = tmp_path / "mixed.csv"
+    f.write_text("algorithm,buffer_size_bytes,iteration,delay,runtime_ms,BW(GB/s)\n"
+                 "stragglar,1048576,1,5.000,6.000,1.0\n"
+                 "ring,1048576,1,-1.000,2.000,1.0,8,float32,tma,2000.0,0.5,0.9,0.800,0.000\n"
+                 "rsag:blocks=64,1048576,1,5.000,7.500,1.0,8,float32,tma,7500.0,0.4,0.7,0.700,5.005,123.4\n"
+                 "Rank 0, done\n")
+    sm.main([str(f)])
+    out = capsys.readouterr().out
+    rows = {l.split()[1]: l.split() for l in out.strip().splitlines()[1:]}
+    assert abs(float(rows["stragglar/ref"][5]) - 1.0) < 1e-9            # nominal delay taken off the reference's row
+    assert abs(float(rows["rsag:blocks=64/tma"][5]) - 2.495) < 1e-9     # measured delay taken off
+    assert rows["rsag:blocks=64/tma"][8] == "123.4" and rows["ring/tma"][8] == "nan"
